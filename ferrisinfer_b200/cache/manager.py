@@ -40,7 +40,7 @@ from typing import Any, Optional
 import torch
 
 from ..errors import CacheError, OutOfPages
-from ..parts.base import FixedState, LayerCache, PagedKV
+from ..parts.base import CombinedNeed, FixedState, LayerCache, PagedKV, leaf_needs
 from .pages import PagePool
 
 NO_PAGE = -1
@@ -144,8 +144,12 @@ def _build_paged(manager, index, need):
         # one page beyond the pool's: the padding page.  Keys and values are the two planes of one tensor, so that
         # a kernel can fetch a tile of keys and the tile of values of the same tokens with one copy.
         shape = (2, g.pool.num_pages + 1, need.num_kv_heads, manager.page_size, need.head_dim)
-        planes = torch.zeros(shape, dtype=manager.dtype, device=manager.device)
-        cache.k, cache.v = planes[0], planes[1]
+        if need.value_dim == need.head_dim:
+            planes = torch.zeros(shape, dtype=manager.dtype, device=manager.device)
+            cache.k, cache.v = planes[0], planes[1]
+        else:  # value heads of another size: two tensors
+            cache.k = torch.zeros(shape[1:], dtype=manager.dtype, device=manager.device)
+            cache.v = torch.zeros((*shape[1:4], need.value_dim), dtype=manager.dtype, device=manager.device)
     return cache
 
 
@@ -153,8 +157,13 @@ def _build_state(manager, index, need):
     return LayerCache(need=need, state=manager.new_state(need.shape, need.dtype))
 
 
+def _build_combined(manager, index, need):
+    return LayerCache(need=need, parts=[None if n is None else manager.build_cache(index, n) for n in need.needs])
+
+
 register_cache_need(PagedKV, _build_paged)
 register_cache_need(FixedState, _build_state)
+register_cache_need(CombinedNeed, _build_combined)
 
 
 class CacheManager:
@@ -180,12 +189,8 @@ class CacheManager:
         self._by_need: dict = {}
         self._num_pages = num_pages
         for i, need in enumerate(needs):
-            if need is None:
-                continue
-            builder = next((b for cls, b in _NEED_BUILDERS.items() if isinstance(need, cls)), None)
-            if builder is None:
-                raise CacheError(f"run-order entry {i} has an unknown cache need {need!r}")
-            self.layer_caches[i] = builder(self, i, need)
+            if need is not None:
+                self.layer_caches[i] = self.build_cache(i, need)
         for name, need in (extra_states or {}).items():
             if device is not None:
                 self.state_tensors[name] = self.new_state(need.shape, need.dtype)
@@ -194,7 +199,7 @@ class CacheManager:
         # Pages of prompts are shared only where a page means the same for every layer: all page groups keep
         # every key (no window) and no mixer keeps a state of its own.
         shareable = bool(self.groups) and all(g.window is None for g in self.groups) and not any(
-            isinstance(n, FixedState) for n in needs)
+            isinstance(leaf, FixedState) for n in needs for leaf in leaf_needs(n))
         self.prefix = PrefixIndex() if (prefix_sharing and shareable) else None
         self.min_prefix_share_tokens = int(min_prefix_share_tokens)
         self.keep_finished = bool(keep_finished) and self.prefix is not None
@@ -204,6 +209,20 @@ class CacheManager:
         self.stats = {"shared_tokens": 0, "shared_pages": 0, "revived_pages": 0, "evicted_pages": 0}
 
     # ------------------------------------------------------------------- set-up
+    def build_cache(self, index: int, need) -> LayerCache:
+        """The cache that serves ``need`` of run-order entry ``index``, from the builder registered for its kind."""
+        builder = next((b for cls, b in _NEED_BUILDERS.items() if isinstance(need, cls)), None)
+        if builder is None:
+            raise CacheError(f"run-order entry {index} has an unknown cache need {need!r}")
+        return builder(self, index, need)
+
+    def _state_tensors_of_layers(self) -> list:
+        out = []
+        for cache in self.layer_caches:
+            if cache is not None:
+                out += [leaf.state for leaf in cache.leaves() if leaf.state is not None]
+        return out
+
     def page_group(self, need: PagedKV) -> PageGroup:
         """The page group of ``need`` (made at its first call): entries with the same need share page ids."""
         gid = self._by_need.get(need)
@@ -233,9 +252,8 @@ class CacheManager:
     def state_bytes(self) -> int:
         """Bytes of the per-request state tensors (mixers' and the engine's)."""
         total = 0
-        for cache in self.layer_caches:
-            if cache is not None and cache.state is not None:
-                total += cache.state.numel() * cache.state.element_size()
+        for t in self._state_tensors_of_layers():
+            total += t.numel() * t.element_size()
         for t in self.state_tensors.values():
             total += t.numel() * t.element_size()
         return total
@@ -286,9 +304,8 @@ class CacheManager:
                 rc.num_tokens = rc.shared_tokens = len(found) * ps
                 self.stats["shared_tokens"] += rc.shared_tokens
                 self.stats["shared_pages"] += len(found) * len(self.groups)
-        for cache in self.layer_caches:
-            if cache is not None and cache.state is not None:
-                cache.state[slot].zero_()
+        for t in self._state_tensors_of_layers():
+            t[slot].zero_()
         for t in self.state_tensors.values():
             t[slot].zero_()
         return rc

@@ -2,7 +2,7 @@
 
 The reference has no registry: it matches ``model_type`` in two places and
 rejects everything but "qwen2" (crates/ferrisinfer-io/src/hf.rs:306-313,
-371-378, 502-510).  Here ``architectures[0]`` of config.json selects an entry;
+371-378, 502-510).  Here ``architectures[0]`` of config.json (or its ``architecture``, a single name) selects an entry;
 an entry gives the typed configuration class (``from_dict`` / ``to_dict``) and a
 function from a configuration to a ``ModelPlan`` (the description of layers,
 parts and run order that ``parts.model.build_model`` turns into a model).
@@ -53,6 +53,10 @@ def get_architecture(name: str) -> Architecture:
 
 
 def architecture_name_of(config_dict: dict) -> str:
+    """``architectures[0]`` of the dict, or its ``architecture`` where a folder names just one."""
+    one = config_dict.get("architecture")
+    if "architectures" not in config_dict and isinstance(one, str) and one:
+        return one
     archs = config_dict.get("architectures")
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
         raise ConfigError("config.json: 'architectures' must be a non-empty list of strings")

@@ -324,3 +324,230 @@ FERRIS_API int ferris_rotary_angles(const int* positions, const float* inv_freq,
 }
 
 FERRIS_TIMELINE_TU(elementwise)
+
+// ---------------------------------------------------------------------------------------------
+// Embedding with a scale and an additive sinusoidal position vector, into the fp32 residual stream:
+//   out[t, 2i] = table[id, 2i] * scale + sin(float(pos_t) * f_i),  out[t, 2i+1] = table[id, 2i+1] * scale + cos(same)
+// f (one frequency per pair of columns) comes from the host, which forms base^(-2i / hidden) in 64-bit and rounds
+// once; the angle and its sine and cosine are fp32.  Ids outside [0, vocab) are reported as by embed_gather.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_sinusoid_kernel(const T* __restrict__ table, const int* ids, const int* positions,
+                                      const float* __restrict__ freq, float scale, float* __restrict__ out, int hidden,
+                                      int vocab, int* status) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    const float pos = (float)positions[t];
+    float* o = out + (size_t)t * hidden;
+    const bool ok = id >= 0 && id < vocab;
+    if (!ok && threadIdx.x == 0 && status) atomicCAS(status, 0, t + 1);
+    const T* row = table + (size_t)(ok ? id : 0) * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float angle = pos * freq[i >> 1];
+        const float pe = (i & 1) ? cosf(angle) : sinf(angle);
+        o[i] = ok ? fmaf(to_float(row[i]), scale, pe) : 0.0f;
+    }
+}
+
+FERRIS_API int ferris_embed_sinusoid(const void* table, int dtype, const int* ids, const int* positions,
+                                     const float* freq, float scale, float* out, int tokens, int hidden, int vocab,
+                                     int* status, void* stream) {
+    if (tokens <= 0) return FERRIS_OK;
+    if (hidden <= 0 || vocab <= 0) FERRIS_REFUSE("embed_sinusoid: hidden=%d vocab=%d", hidden, vocab);
+    const int threads = hidden >= 1024 ? 256 : 128;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == FERRIS_F32)
+        ferris_launch(embed_sinusoid_kernel<float>, dim3(tokens), dim3(threads), 0, s, (const float*)table, ids, positions,
+                      freq, scale, out, hidden, vocab, status);
+    else if (dtype == FERRIS_BF16)
+        ferris_launch(embed_sinusoid_kernel<bf16>, dim3(tokens), dim3(threads), 0, s, (const bf16*)table, ids, positions,
+                      freq, scale, out, hidden, vocab, status);
+    else
+        FERRIS_REFUSE("embed_sinusoid: unknown dtype %d", dtype);
+    FERRIS_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------------------------
+// RMSNorm in groups: a row of `hidden` is cut into `groups` equal consecutive parts, each part is divided by its
+// own sqrt(mean(part^2) + eps), and the whole is multiplied by w.  A warp per (row, group); statistics fp32.
+// ---------------------------------------------------------------------------------------------
+template <typename TOut>
+__global__ void __launch_bounds__(256) grouped_rmsnorm_kernel(const float* x, const float* __restrict__ w,
+                                                              const int* __restrict__ row_index, TOut* __restrict__ out,
+                                                              int rows, int hidden, int groups, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (item >= (long long)rows * groups) return;
+    const int r = (int)(item / groups), g = (int)(item % groups);
+    const int n = hidden / groups;
+    const int src = row_index ? row_index[r] : r;
+    const float* xr = x + (size_t)src * hidden + (size_t)g * n;
+    float ss = 0.0f;
+    for (int i = lane; i < n; i += 32) {
+        const float v = xr[i];
+        ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)n + eps);
+    TOut* o = out + (size_t)r * hidden + (size_t)g * n;
+    const float* wg = w + (size_t)g * n;
+    for (int i = lane; i < n; i += 32) o[i] = from_float<TOut>((xr[i] * inv) * wg[i]);
+}
+
+FERRIS_API int ferris_grouped_rmsnorm(const float* x, const float* w, const int* row_index, void* out, int out_dtype,
+                                      int rows, int hidden, int groups, float eps, void* stream) {
+    if (rows <= 0) return FERRIS_OK;
+    if (hidden <= 0 || groups <= 0 || hidden % groups) FERRIS_REFUSE("grouped rmsnorm: %d columns in %d groups", hidden, groups);
+    const long long items = (long long)rows * groups;
+    const dim3 grid((unsigned)((items + 7) / 8)), block(256);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == FERRIS_F32)
+        ferris_launch(grouped_rmsnorm_kernel<float>, grid, block, 0, s, x, w, row_index, (float*)out, rows, hidden, groups, eps);
+    else if (out_dtype == FERRIS_BF16)
+        ferris_launch(grouped_rmsnorm_kernel<bf16>, grid, block, 0, s, x, w, row_index, (bf16*)out, rows, hidden, groups, eps);
+    else
+        FERRIS_REFUSE("grouped rmsnorm: unknown dtype %d", out_dtype);
+    FERRIS_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------------------------
+// h += x over n fp32 values (the embedding output that a repeated pass of a looped model takes in again).
+// ---------------------------------------------------------------------------------------------
+__global__ void add_f32_kernel(float* h, const float* x, long long n) {
+    pdl_wait();
+    pdl_launch_dependents();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        h[i] += x[i];
+}
+
+FERRIS_API int ferris_add_f32(float* h, const float* x, long long n, void* stream) {
+    if (n <= 0) return FERRIS_OK;
+    const int threads = 256;
+    const long long want = (n + threads - 1) / threads;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    ferris_launch(add_f32_kernel, dim3(blocks), dim3(threads), 0, (cudaStream_t)stream, h, x, n);
+    FERRIS_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Activations of a plain (ungated) feed-forward, out[i] = a(in[i]), fp32 arithmetic.
+//   kind 0, xIELU with two learned numbers (p, q) in `params`:
+//     z > 0:  softplus(p) z^2 + z / 2;   z <= 0:  (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2
+//   kind 1, SiLU: z / (1 + exp(-z)).
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float softplus_f(float v) { return v > 20.0f ? v : log1pf(expf(v)); }
+
+template <typename T>
+__global__ void activation_kernel(const T* in, T* out, long long n, int kind,
+                                  const float* __restrict__ params) {
+    pdl_wait();
+    pdl_launch_dependents();
+    float a = 0.0f, b = 0.0f;
+    if (kind == 0) {
+        a = softplus_f(params[0]);
+        b = 0.5f + softplus_f(params[1]);
+    }
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const float z = to_float(in[i]);
+        float r;
+        if (kind == 0)
+            r = z > 0.0f ? fmaf(a * z, z, 0.5f * z) : fmaf(b, expm1f(z) - z, 0.5f * z);
+        else
+            r = z / (1.0f + expf(-z));
+        out[i] = from_float<T>(r);
+    }
+}
+
+FERRIS_API int ferris_activation(const void* in, void* out, int dtype, long long n, int kind, const float* params,
+                                 void* stream) {
+    if (n <= 0) return FERRIS_OK;
+    if (kind < 0 || kind > 1) FERRIS_REFUSE("activation: unknown kind %d", kind);
+    if (kind == 0 && !params) FERRIS_REFUSE("activation: xIELU needs its two numbers");
+    const int threads = 256;
+    const long long want = (n + threads - 1) / threads;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == FERRIS_F32)
+        ferris_launch(activation_kernel<float>, dim3(blocks), dim3(threads), 0, s, (const float*)in, (float*)out, n, kind, params);
+    else if (dtype == FERRIS_BF16)
+        ferris_launch(activation_kernel<bf16>, dim3(blocks), dim3(threads), 0, s, (const bf16*)in, (bf16*)out, n, kind, params);
+    else
+        FERRIS_REFUSE("activation: unknown dtype %d", dtype);
+    FERRIS_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------------------------
+// What stands between the q/k/v product and attention where positions do not rotate anything:
+//   q and k heads divided by their own sqrt(mean(.^2) + eps) when `unit_norm` (an RMS norm without a weight);
+//   q multiplied by a temperature that grows with the position, 1 + coef * ln(floor((pos + 1) / every) + 1),
+//   when every > 0; k and v stored into the paged cache (k heads of d, v heads of dv).
+// qkv rows: [nh d | nkv d | nkv dv]; q is rewritten in place.  One block per token, a warp per head in turn.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128) qk_prepare_cache_write_kernel(
+    T* __restrict__ qkv, int ld, const int* __restrict__ positions, const int* __restrict__ slot_mapping,
+    T* __restrict__ k_cache, T* __restrict__ v_cache, int nh, int nkv, int d, int dv, int page_size, int unit_norm,
+    float eps, float temp_coef, int temp_every, int write_kv) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const int pos = positions[t];
+    T* row = qkv + (size_t)t * ld;
+    const int slot = write_kv ? slot_mapping[t] : -1;
+    const int page = slot >= 0 ? slot / page_size : 0;
+    const int in_page = slot >= 0 ? slot % page_size : 0;
+    const float temp = temp_every > 0 ? 1.0f + temp_coef * logf((float)((pos + 1) / temp_every) + 1.0f) : 1.0f;
+    for (int h = warp; h < nh + nkv; h += warps) {
+        T* x = row + (size_t)h * d;
+        float ss = 0.0f;
+        if (unit_norm) {
+            for (int i = lane; i < d; i += 32) {
+                const float v = to_float(x[i]);
+                ss = fmaf(v, v, ss);
+            }
+            ss = warp_sum(ss);
+        }
+        float f = unit_norm ? 1.0f / sqrtf(ss / (float)d + eps) : 1.0f;
+        if (h < nh) {
+            f *= temp;
+            for (int i = lane; i < d; i += 32) x[i] = from_float<T>(to_float(x[i]) * f);
+        } else if (slot >= 0) {
+            T* kc = k_cache + (((size_t)page * nkv + (h - nh)) * page_size + in_page) * d;
+            for (int i = lane; i < d; i += 32) kc[i] = from_float<T>(to_float(x[i]) * f);
+        }
+    }
+    if (slot < 0) return;
+    const T* vrow = row + (size_t)(nh + nkv) * d;
+    for (int w = threadIdx.x; w < nkv * dv; w += blockDim.x) {
+        const int h = w / dv, i = w % dv;
+        v_cache[(((size_t)page * nkv + h) * page_size + in_page) * dv + i] = vrow[w];
+    }
+}
+
+FERRIS_API int ferris_qk_prepare_cache_write(void* qkv, int ld, int dtype, const int* positions, const int* slot_mapping,
+                                             void* k_cache, void* v_cache, int tokens, int nh, int nkv, int d, int dv,
+                                             int page_size, int unit_norm, float eps, float temp_coef, int temp_every,
+                                             int write_kv, void* stream) {
+    if (tokens <= 0) return FERRIS_OK;
+    if (nh <= 0 || nkv <= 0 || d <= 0 || dv <= 0 || page_size <= 0)
+        FERRIS_REFUSE("qk_prepare: nh=%d nkv=%d d=%d dv=%d page_size=%d", nh, nkv, d, dv, page_size);
+    if (ld < (nh + nkv) * d + nkv * dv) FERRIS_REFUSE("qk_prepare: rows of %d are too short", ld);
+    if (write_kv && (!slot_mapping || !k_cache || !v_cache)) FERRIS_REFUSE("qk_prepare: no cache to write");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == FERRIS_F32)
+        ferris_launch(qk_prepare_cache_write_kernel<float>, dim3(tokens), dim3(128), 0, s, (float*)qkv, ld, positions,
+                      slot_mapping, (float*)k_cache, (float*)v_cache, nh, nkv, d, dv, page_size, unit_norm, eps, temp_coef,
+                      temp_every, write_kv);
+    else if (dtype == FERRIS_BF16)
+        ferris_launch(qk_prepare_cache_write_kernel<bf16>, dim3(tokens), dim3(128), 0, s, (bf16*)qkv, ld, positions,
+                      slot_mapping, (bf16*)k_cache, (bf16*)v_cache, nh, nkv, d, dv, page_size, unit_norm, eps, temp_coef,
+                      temp_every, write_kv);
+    else
+        FERRIS_REFUSE("qk_prepare: unknown dtype %d", dtype);
+    FERRIS_LAUNCH_CHECK();
+}

@@ -119,10 +119,11 @@ class Engine:
     def _pages_that_fit(self, needs, page_size, fraction, sc) -> int:
         """Pages per group that ``fraction`` of the free device memory holds, after what the per-request state of
         fixed size (mixers' and the sampler's, one row per request slot and one more) takes from it."""
-        from ..parts.base import FixedState, PagedKV
+        from ..parts.base import FixedState, PagedKV, leaf_needs
 
+        needs = [leaf for n in needs for leaf in leaf_needs(n)]
         item = 2 if self.dtype == torch.bfloat16 else 4
-        per_page = sum(2 * n.num_kv_heads * n.head_dim * page_size * item for n in needs if isinstance(n, PagedKV))
+        per_page = sum(n.num_kv_heads * (n.head_dim + n.value_dim) * page_size * item for n in needs if isinstance(n, PagedKV))
         if per_page == 0:
             return 1
         states = [n for n in needs if isinstance(n, FixedState)] + [RNG_NEED]

@@ -23,7 +23,7 @@ import numpy as np
 import torch
 
 PAGE_SIZE = 16
-MAX_LIVE_REQUESTS = 16
+MAX_LIVE_REQUESTS = 4  # state slots: no more requests are live at any time, so slots are used again
 
 
 def build_parser() -> argparse.ArgumentParser:

@@ -651,10 +651,11 @@ def rope_cache_write(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: Optio
 def paged_attention_simt(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                          block_tables: torch.Tensor, token_seq: torch.Tensor, positions: torch.Tensor,
                          num_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float,
-                         score_slopes: Optional[torch.Tensor] = None):
+                         score_slopes: Optional[torch.Tensor] = None, v_head_dim: Optional[int] = None):
     """General attention over the paged cache; q is read from the first nh*d columns of ``qkv``.
     ``score_slopes`` (fp32 [num_heads]): the score of a query at position P and the key at position j gets
-    slopes[head] * (j - P) added."""
+    slopes[head] * (j - P) added.  ``v_head_dim``: size of a value head where it differs from the keys'."""
+    dv = int(v_head_dim or head_dim)
     T, _, ldq = _rows(qkv, "attention queries")
     T2, width, ldo = _rows(out, "attention output")
     _need(k_cache, "key cache", qkv.dtype)
@@ -662,10 +663,11 @@ def paged_attention_simt(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Te
     _need(block_tables, "block tables", torch.int32)
     _need(token_seq, "token-to-request map", torch.int32)
     _need(positions, "positions", torch.int32)
-    if T != T2 or width != num_heads * head_dim or out.dtype != qkv.dtype or qkv.shape[1] < num_heads * head_dim:
+    if T != T2 or width != num_heads * dv or out.dtype != qkv.dtype or qkv.shape[1] < num_heads * head_dim:
         raise KernelError(f"attention: q {tuple(qkv.shape)}, out {tuple(out.shape)}")
-    if k_cache.dim() != 4 or k_cache.shape[1] != num_kv_heads or k_cache.shape[3] != head_dim or block_tables.dim() != 2:
-        raise KernelError(f"attention: cache {tuple(k_cache.shape)}, tables {tuple(block_tables.shape)}")
+    if (k_cache.dim() != 4 or k_cache.shape[1] != num_kv_heads or k_cache.shape[3] != head_dim or block_tables.dim() != 2
+            or v_cache.shape != (*k_cache.shape[:3], dv)):
+        raise KernelError(f"attention: caches {tuple(k_cache.shape)} {tuple(v_cache.shape)}, tables {tuple(block_tables.shape)}")
     if score_slopes is not None:
         _need(score_slopes, "score slopes", torch.float32)
         if score_slopes.numel() != num_heads:
@@ -674,9 +676,180 @@ def paged_attention_simt(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Te
         _lib().ferris_paged_attention_simt(_ptr(qkv), _c_int(ldq), _ptr(out), _c_int(ldo), _ptr(k_cache), _ptr(v_cache),
                                            _dt(qkv, "attention"), _ptr(block_tables), _c_int(block_tables.shape[1]),
                                            _ptr(token_seq), _ptr(positions), _c_int(T), _c_int(num_heads),
-                                           _c_int(num_kv_heads), _c_int(head_dim), _c_int(k_cache.shape[2]),
+                                           _c_int(num_kv_heads), _c_int(head_dim), _c_int(dv), _c_int(k_cache.shape[2]),
                                            _c_int(window or 0), _c_float(scale), _ptr(score_slopes), _stream()),
         "paged attention",
+    )
+
+
+def embed_sinusoid(table: torch.Tensor, ids: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor, scale: float,
+                   out: torch.Tensor, status: Optional[torch.Tensor] = None):
+    """out[t, :] = table[ids[t], :] * scale + pe(positions[t]) as fp32, pe[2i] = sin(pos * freq[i]), pe[2i + 1] = cos(same)."""
+    _need(table, "embedding table")
+    _need(ids, "token ids", torch.int32)
+    _need(positions, "positions", torch.int32)
+    _need(freq, "position frequencies", torch.float32)
+    _need(out, "embedding output", torch.float32)
+    T, H = out.shape
+    if table.dim() != 2 or table.shape[1] != H or ids.numel() != T or positions.numel() != T or freq.numel() != (H + 1) // 2:
+        raise KernelError(f"embed_sinusoid: table {tuple(table.shape)}, ids {tuple(ids.shape)}, out {tuple(out.shape)}, "
+                          f"{freq.numel()} frequencies")
+    _check(
+        _lib().ferris_embed_sinusoid(_ptr(table), _c_int(_dt(table, "embedding table")), _ptr(ids), _ptr(positions),
+                                     _ptr(freq), _c_float(scale), _ptr(out), _c_int(T), _c_int(H), _c_int(table.shape[0]),
+                                     _ptr(status), _stream()),
+        "embed_sinusoid",
+    )
+
+
+def grouped_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, groups: int, out: torch.Tensor,
+                    row_index: Optional[torch.Tensor] = None):
+    """RMSNorm in ``groups`` equal consecutive parts of each row, each with a root mean square of its own; then the
+    whole times ``weight``.  One group: the plain kernel."""
+    if groups == 1:
+        return rmsnorm(x, weight, eps, out, row_index)
+    _need(x, "rmsnorm input", torch.float32)
+    _need(weight, "rmsnorm weight", torch.float32)
+    _need(out, "rmsnorm output")
+    rows, H = out.shape
+    if x.shape[1] != H or weight.numel() != H or groups < 1 or H % groups:
+        raise KernelError(f"grouped rmsnorm: x {tuple(x.shape)}, weight {tuple(weight.shape)}, {groups} groups")
+    if row_index is not None:
+        _need(row_index, "rmsnorm row index", torch.int32)
+        if row_index.numel() != rows:
+            raise KernelError("rmsnorm: one row index per output row is needed")
+    elif x.shape[0] != rows:
+        raise KernelError("rmsnorm: input and output row counts differ")
+    _check(
+        _lib().ferris_grouped_rmsnorm(_ptr(x), _ptr(weight), _ptr(row_index), _ptr(out), _c_int(_dt(out, "rmsnorm output")),
+                                      _c_int(rows), _c_int(H), _c_int(groups), _c_float(eps), _stream()),
+        "grouped rmsnorm",
+    )
+
+
+def add_(h: torch.Tensor, x: torch.Tensor):
+    """h += x, both fp32 and of one shape."""
+    _need(h, "sum", torch.float32)
+    _need(x, "addend", torch.float32)
+    if h.shape != x.shape:
+        raise KernelError(f"add: {tuple(h.shape)} += {tuple(x.shape)}")
+    _check(_lib().ferris_add_f32(_ptr(h), _ptr(x), ctypes.c_longlong(h.numel()), _stream()), "add")
+
+
+ACTIVATIONS = {"xielu": 0, "silu": 1}
+
+
+def activation(x: torch.Tensor, out: torch.Tensor, kind: str, params: Optional[torch.Tensor] = None):
+    """out = a(x) element by element (``out`` may be ``x``).  ``xielu``: with softplus of the two numbers of
+    ``params`` (fp32 [2]) as a = softplus(p), b = 1/2 + softplus(q): a z^2 + z / 2 for z > 0, b (exp(z) - 1 - z) + z / 2
+    otherwise.  ``silu``: z sigmoid(z)."""
+    _need(x, "activation input")
+    _need(out, "activation output", x.dtype)
+    if kind not in ACTIVATIONS or out.shape != x.shape:
+        raise KernelError(f"activation '{kind}': {tuple(x.shape)} -> {tuple(out.shape)}")
+    if params is not None:
+        _need(params, "activation parameters", torch.float32)
+    if kind == "xielu" and (params is None or params.numel() != 2):
+        raise KernelError("activation xielu: two numbers are needed")
+    _check(_lib().ferris_activation(_ptr(x), _ptr(out), _c_int(_dt(x, "activation")), ctypes.c_longlong(x.numel()),
+                                    _c_int(ACTIVATIONS[kind]), _ptr(params), _stream()), "activation")
+
+
+def qk_prepare_cache_write(qkv: torch.Tensor, positions: torch.Tensor, slot_mapping: Optional[torch.Tensor],
+                           k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], num_heads: int,
+                           num_kv_heads: int, head_dim: int, v_head_dim: int, unit_norm_eps: Optional[float],
+                           temperature: Optional[tuple], write_kv: bool = True):
+    """Between the q/k/v product and attention where nothing rotates: q and k heads divided by their root mean
+    square (``unit_norm_eps`` not None), q times 1 + coef * ln(floor((pos + 1) / every) + 1) (``temperature`` =
+    (coef, every)), k and v into the paged cache.  ``qkv`` rows are [nh d | nkv d | nkv dv]; q is rewritten in place."""
+    T, width, ld = _rows(qkv, "qkv")
+    _need(positions, "positions", torch.int32)
+    if width != (num_heads + num_kv_heads) * head_dim + num_kv_heads * v_head_dim or positions.numel() != T:
+        raise KernelError(f"qk_prepare: qkv {tuple(qkv.shape)} for {num_heads}+{num_kv_heads} heads of {head_dim} and "
+                          f"{num_kv_heads} of {v_head_dim}")
+    page_size = 1
+    if write_kv:
+        _need(slot_mapping, "slot mapping", torch.int32)
+        _need(k_cache, "key cache", qkv.dtype)
+        _need(v_cache, "value cache", qkv.dtype)
+        page_size = k_cache.shape[2]
+        if (slot_mapping.numel() != T or k_cache.shape[1:] != (num_kv_heads, page_size, head_dim)
+                or v_cache.shape != (*k_cache.shape[:3], v_head_dim)):
+            raise KernelError(f"qk_prepare: caches {tuple(k_cache.shape)} {tuple(v_cache.shape)} do not fit")
+    coef, every = temperature if temperature else (0.0, 0)
+    _check(
+        _lib().ferris_qk_prepare_cache_write(_ptr(qkv), _c_int(ld), _c_int(_dt(qkv, "qkv")), _ptr(positions),
+                                             _ptr(slot_mapping if write_kv else None), _ptr(k_cache if write_kv else None),
+                                             _ptr(v_cache if write_kv else None), _c_int(T), _c_int(num_heads),
+                                             _c_int(num_kv_heads), _c_int(head_dim), _c_int(v_head_dim), _c_int(page_size),
+                                             _c_int(0 if unit_norm_eps is None else 1), _c_float(unit_norm_eps or 0.0),
+                                             _c_float(coef), _c_int(int(every)), _c_int(1 if write_kv else 0), _stream()),
+        "qk_prepare_cache_write",
+    )
+
+
+def short_conv(y: torch.Tensor, out: torch.Tensor, weight: torch.Tensor, state: Optional[torch.Tensor], ctx,
+               advance: bool = True):
+    """out = y + causal convolution of y over time on each channel (``weight`` fp32 [channels, taps]), a request's
+    ``taps - 1`` inputs before the step taken from ``state`` (fp32 [slots, taps - 1, channels]) and, with
+    ``advance``, the state moved on to the step's end.  ``ctx``: the step context (device arrays only)."""
+    T, C, ldy = _rows(y, "convolution input")
+    T2, C2, ldo = _rows(out, "convolution output")
+    _need(weight, "convolution weight", torch.float32)
+    taps = weight.shape[1]
+    if (T2, C2) != (T, C) or out.dtype != y.dtype or weight.shape != (C, taps) or y.data_ptr() == out.data_ptr():
+        raise KernelError(f"short conv: y {tuple(y.shape)}, out {tuple(out.shape)}, weight {tuple(weight.shape)}")
+    if taps > 1:
+        _need(state, "convolution state", torch.float32)
+        if state.shape[1:] != (taps - 1, C):
+            raise KernelError(f"short conv: state {tuple(state.shape)} for {taps} taps of {C} channels")
+    kernels = 2 if (advance and taps > 1) else 1
+    _check(
+        _lib().ferris_short_conv(_ptr(y), _c_int(ldy), _ptr(out), _c_int(ldo), _c_int(_dt(y, "short conv")), _ptr(weight),
+                                 _ptr(state if taps > 1 else None), _ptr(ctx.token_seq), _ptr(ctx.positions),
+                                 _ptr(ctx.seq_q_start), _ptr(ctx.seq_start_pos), _ptr(ctx.seq_state_slot), _c_int(T),
+                                 _c_int(ctx.num_seqs), _c_int(C), _c_int(taps), _c_int(1 if advance else 0), _stream()),
+        "short conv", kernels,
+    )
+
+
+def linear_attention(qkv: torch.Tensor, offsets: tuple, out: torch.Tensor, state: torch.Tensor, decay: torch.Tensor,
+                     ctx, heads: int, dim: int, vdim: int, silu: bool = False, write_state: bool = True):
+    """Decayed linear attention of the step's tokens, request by request from each request's state:
+    S <- decay[h] S + k v^T, o = S^T q per head.  ``qkv`` rows hold q, k heads (heads x dim) and v heads
+    (heads x vdim) at the column ``offsets`` (q, k, v); ``out`` fp32 [T, heads x vdim]; ``state`` fp32
+    [slots, heads, vdim, dim].  ``silu``: q, k and v pass through SiLU on the way in."""
+    T, width, ld = _rows(qkv, "linear attention input")
+    T2, n, ldo = _rows(out, "linear attention output")
+    _need(state, "linear attention state", torch.float32)
+    _need(decay, "decays", torch.float32)
+    q_off, k_off, v_off = (int(o) for o in offsets)
+    if (T2 != T or out.dtype != torch.float32 or n != heads * vdim or state.shape[1:] != (heads, vdim, dim)
+            or decay.numel() != heads or max(q_off, k_off) + heads * dim > width or v_off + heads * vdim > width):
+        raise KernelError(f"linear attention: qkv {tuple(qkv.shape)}, out {tuple(out.shape)}, state {tuple(state.shape)}")
+    _check(
+        _lib().ferris_linear_attention(_ptr(qkv), _c_int(ld), _c_int(q_off), _c_int(k_off), _c_int(v_off),
+                                       _c_int(_dt(qkv, "linear attention")), _ptr(out), _c_int(ldo), _ptr(state),
+                                       _ptr(decay), _ptr(ctx.seq_q_start), _ptr(ctx.seq_state_slot), _c_int(ctx.num_seqs),
+                                       _c_int(heads), _c_int(dim), _c_int(vdim), _c_int(1 if silu else 0),
+                                       _c_int(1 if write_state else 0), _stream()),
+        "linear attention",
+    )
+
+
+def gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor):
+    """out = rmsnorm(o) * weight * sigmoid(gate), row by row; o fp32, gate and out in the activations' type."""
+    T, n, ldi = _rows(o, "gated norm input")
+    T2, n2, ldg = _rows(gate, "gate")
+    T3, n3, ldo = _rows(out, "gated norm output")
+    _need(weight, "gated norm weight", torch.float32)
+    if (o.dtype != torch.float32 or (T2, n2) != (T, n) or (T3, n3) != (T, n) or gate.dtype != out.dtype
+            or weight.numel() != n):
+        raise KernelError(f"gated rmsnorm: o {tuple(o.shape)}, gate {tuple(gate.shape)}, out {tuple(out.shape)}")
+    _check(
+        _lib().ferris_gated_rmsnorm(_ptr(o), _c_int(ldi), _ptr(gate), _c_int(ldg), _ptr(weight), _ptr(out), _c_int(ldo),
+                                    _c_int(_dt(out, "gated norm")), _c_int(T), _c_int(n), _c_float(eps), _stream()),
+        "gated rmsnorm",
     )
 
 
@@ -830,14 +1003,19 @@ def attention_step(qkv, out, k_cache, v_cache, meta, ctx, num_heads, num_kv_head
 
 
 def paged_attention(qkv, out, k_cache, v_cache, block_tables, ctx, num_heads, num_kv_heads, head_dim, window, scale,
-                    score_slopes: Optional[torch.Tensor] = None):
+                    score_slopes: Optional[torch.Tensor] = None, v_head_dim: Optional[int] = None):
     """Attention of the step's tokens over the paged cache (their own keys are in it already).
     ``ctx`` is the step context.  bf16 with head size 64 / 128 runs on the tensor cores: the split-KV
     kernel when every request brings one token, the prefill kernel otherwise; every other geometry, the
-    32-bit path, and scores with slopes added (``score_slopes``) run the general kernel."""
+    32-bit path, scores with slopes added (``score_slopes``) and value heads of another size than the keys'
+    (``v_head_dim``) run the general kernel."""
     _need(k_cache, "key cache", qkv.dtype)
     _need(v_cache, "value cache", qkv.dtype)
     _need(block_tables, "block tables", torch.int32)
+    if v_head_dim is not None and v_head_dim != head_dim:
+        paged_attention_simt(qkv, out, k_cache, v_cache, block_tables, ctx.token_seq, ctx.positions, num_heads,
+                             num_kv_heads, head_dim, window, scale, score_slopes=score_slopes, v_head_dim=v_head_dim)
+        return
     if k_cache.dim() != 4 or k_cache.shape[1] != num_kv_heads or k_cache.shape[3] != head_dim \
             or v_cache.shape != k_cache.shape or block_tables.dim() != 2:
         raise KernelError(f"attention: cache {tuple(k_cache.shape)}, tables {tuple(block_tables.shape)}")

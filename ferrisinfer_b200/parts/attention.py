@@ -13,6 +13,14 @@ Unlike the reference, the step's keys and values are written to the cache BEFORE
 attention kernel runs, so one kernel serves whole prompts, portions and decoded tokens alike,
 and q, k, v come from one fused [Q + 2 KV, H] matrix product.  ``window`` (keys the query sees,
 itself included; None = all) is a parameter, as are the scale and every size.
+
+Options beyond the reference's layer, each a parameter of its own:
+  ``v_head_dim``        value heads of another size than query and key heads
+  ``qk_unit_norm_eps``  q and k heads divided by their own sqrt(mean(.^2) + eps), no weight
+  ``query_temperature`` (coef, every): q at position p times 1 + coef * ln(floor((p + 1) / every) + 1)
+  ``tensor_names``      the folder's names of the four matrices under the prefix (then no biases are read)
+With any of the first three the step runs product -> norm / temperature / cache write -> attention -> product;
+the position encoding must then be one that rotates nothing (it may add slopes to the scores).
 """
 
 from __future__ import annotations
@@ -36,37 +44,64 @@ class GroupedQueryAttention(Mixer):
         return bool(getattr(self.position, "graph_safe", False))
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
-                 position: PartSpec, window: Optional[int] = None, scale: Optional[float] = None):
+                 position: PartSpec, window: Optional[int] = None, scale: Optional[float] = None,
+                 v_head_dim: Optional[int] = None, qk_unit_norm_eps: Optional[float] = None,
+                 query_temperature: Optional[tuple] = None, tensor_names: Optional[dict] = None):
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} heads cannot share {num_kv_heads} kv heads")
         self.hidden_size, self.num_heads = int(hidden_size), int(num_heads)
         self.num_kv_heads, self.head_dim = int(num_kv_heads), int(head_dim)
+        self.v_head_dim = self.head_dim if v_head_dim is None else int(v_head_dim)
         self.window = None if window is None else int(window)
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.head_dim)
         self.position = build_part("position", position) if isinstance(position, PartSpec) else position
+        self.qk_unit_norm_eps = None if qk_unit_norm_eps is None else float(qk_unit_norm_eps)
+        self.query_temperature = None
+        if query_temperature is not None:
+            coef, every = query_temperature
+            if int(every) <= 0:
+                raise ValueError(f"the query temperature grows every {every} positions: a positive count is needed")
+            self.query_temperature = (float(coef), int(every))
         self.q_size = self.num_heads * self.head_dim
         self.kv_size = self.num_kv_heads * self.head_dim
+        self.v_size = self.num_kv_heads * self.v_head_dim
+        self.o_size = self.num_heads * self.v_head_dim
+        # the plain layer (the reference's) keeps its fused kernels; any option sends the step the general way
+        self.plain = (self.v_head_dim == self.head_dim and self.qk_unit_norm_eps is None
+                      and self.query_temperature is None)
+        if not self.plain and getattr(self.position, "rotary_dim", 0):
+            raise ValueError("unit-norm keys, a query temperature or value heads of their own size go with a "
+                             "position encoding that rotates nothing")
+        self.tensor_names = dict(tensor_names) if tensor_names else None
         self.qkv_weight = self.qkv_bias = self.o_weight = None
 
     # ------------------------------------------------------------------ weights
+    def _matrix_name(self, prefix, which):
+        if self.tensor_names:
+            return f"{prefix}.{self.tensor_names[which]}"
+        return f"{prefix}.{which}_proj.weight"
+
     def tensor_specs(self, prefix):
         H, Q, KV = self.hidden_size, self.q_size, self.kv_size
-        return [
-            TensorSpec(f"{prefix}.q_proj.weight", (Q, H), "matrix"),
-            TensorSpec(f"{prefix}.k_proj.weight", (KV, H), "matrix"),
-            TensorSpec(f"{prefix}.v_proj.weight", (KV, H), "matrix"),
-            TensorSpec(f"{prefix}.q_proj.bias", (Q,), "bias", required=False),
-            TensorSpec(f"{prefix}.k_proj.bias", (KV,), "bias", required=False),
-            TensorSpec(f"{prefix}.v_proj.bias", (KV,), "bias", required=False),
-            TensorSpec(f"{prefix}.o_proj.weight", (H, Q), "matrix"),
+        specs = [
+            TensorSpec(self._matrix_name(prefix, "q"), (Q, H), "matrix"),
+            TensorSpec(self._matrix_name(prefix, "k"), (KV, H), "matrix"),
+            TensorSpec(self._matrix_name(prefix, "v"), (self.v_size, H), "matrix"),
         ]
+        if not self.tensor_names:
+            specs += [
+                TensorSpec(f"{prefix}.q_proj.bias", (Q,), "bias", required=False),
+                TensorSpec(f"{prefix}.k_proj.bias", (KV,), "bias", required=False),
+                TensorSpec(f"{prefix}.v_proj.bias", (self.v_size,), "bias", required=False),
+            ]
+        return specs + [TensorSpec(self._matrix_name(prefix, "o"), (H, self.o_size), "matrix")]
 
     def bind(self, tensors, prefix):
-        w = [tensors.pop(f"{prefix}.{n}_proj.weight") for n in "qkv"]
+        w = [tensors.pop(self._matrix_name(prefix, n)) for n in "qkv"]
         self.qkv_weight = torch.cat(w, dim=0).contiguous()
-        biases = [tensors.pop(f"{prefix}.{n}_proj.bias", None) for n in "qkv"]
+        biases = [None if self.tensor_names else tensors.pop(f"{prefix}.{n}_proj.bias", None) for n in "qkv"]
         if any(b is not None for b in biases):
-            sizes = (self.q_size, self.kv_size, self.kv_size)
+            sizes = (self.q_size, self.kv_size, self.v_size)
             parts = [
                 b if b is not None else torch.zeros(n, dtype=torch.float32, device=self.qkv_weight.device)
                 for b, n in zip(biases, sizes)
@@ -74,18 +109,29 @@ class GroupedQueryAttention(Mixer):
             self.qkv_bias = torch.cat(parts).contiguous()
         else:
             self.qkv_bias = None
-        self.o_weight = tensors[f"{prefix}.o_proj.weight"]
+        self.o_weight = tensors[self._matrix_name(prefix, "o")]
 
     # -------------------------------------------------------------------- cache
     def cache_need(self):
-        return PagedKV(self.num_kv_heads, self.head_dim, self.window)
+        return PagedKV(self.num_kv_heads, self.head_dim, self.window,
+                       None if self.v_head_dim == self.head_dim else self.v_head_dim)
 
     # ------------------------------------------------------------------ forward
     def forward(self, x, h, ctx, cache: LayerCache, owns_cache: bool):
         T = x.shape[0]
         nh, nkv, d = self.num_heads, self.num_kv_heads, self.head_dim
         meta = ctx.paged[cache.group]
-        qkv = ctx.workspace.get("attn_qkv", (T, self.q_size + 2 * self.kv_size), x.dtype)
+        qkv = ctx.workspace.get("attn_qkv", (T, self.q_size + self.kv_size + self.v_size), x.dtype)
+        if not self.plain:
+            dv = self.v_head_dim
+            ops.gemm(x, self.qkv_weight, self.qkv_bias, qkv)
+            ops.qk_prepare_cache_write(qkv, ctx.positions, meta.slot_mapping, cache.k, cache.v, nh, nkv, d, dv,
+                                       self.qk_unit_norm_eps, self.query_temperature, write_kv=owns_cache)
+            out = ctx.workspace.get("attn_out", (T, self.o_size), x.dtype)
+            ops.paged_attention(qkv, out, cache.k, cache.v, meta.block_tables, ctx, nh, nkv, d, self.window or 0,
+                                self.scale, score_slopes=self.position.score_slopes(nh, qkv.device), v_head_dim=dv)
+            ops.gemm(out, self.o_weight, None, h, accumulate=True)
+            return
         table = self.position.rotary_table(qkv.device)
         inv_freq, rotary = table if table is not None else (None, 0)
         slopes = self.position.score_slopes(nh, qkv.device)

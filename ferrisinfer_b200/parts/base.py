@@ -25,11 +25,17 @@ from .plan import TensorSpec
 class PagedKV:
     """The mixer keeps a key and a value of ``num_kv_heads x head_dim`` per token, in pages.
     ``window``: None = every past token is read; n = only the last n (the current one included),
-    so pages that lie wholly behind the window are given back while the request runs."""
+    so pages that lie wholly behind the window are given back while the request runs.
+    ``v_head_dim``: size of a value head where it differs from a key head's (None = the same)."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_head_dim: Optional[int] = None
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
 
 
 @dataclass(frozen=True)
@@ -39,6 +45,26 @@ class FixedState:
 
     shape: tuple
     dtype: torch.dtype = torch.float32
+
+
+@dataclass(frozen=True)
+class CombinedNeed:
+    """Several needs of one mixer (a mixer that wraps another, or one with pages AND a state): the mixer gets a
+    ``LayerCache`` whose ``parts`` are the caches of ``needs``, in order."""
+
+    needs: tuple
+
+
+def leaf_needs(need) -> list:
+    """The needs that ``need`` is made of (itself, unless it is a CombinedNeed); None gives none."""
+    if need is None:
+        return []
+    if isinstance(need, CombinedNeed):
+        out = []
+        for n in need.needs:
+            out += leaf_needs(n)
+        return out
+    return [need]
 
 
 # ----------------------------------------------------------------------------- step context
@@ -98,7 +124,8 @@ class LayerCache:
     """What one run of a layer's mixer owns in the cache.
 
     ``group``: id of the page group (PagedKV) whose block tables address ``k`` and ``v``
-    ([pages, kv heads, page size, head dim]); ``state``: [slots, *shape] for FixedState.
+    ([pages, kv heads, page size, head dim]); ``state``: [slots, *shape] for FixedState; ``parts``: the caches
+    of a CombinedNeed's needs.
     """
 
     need: Any
@@ -106,6 +133,17 @@ class LayerCache:
     k: Optional[torch.Tensor] = None
     v: Optional[torch.Tensor] = None
     state: Optional[torch.Tensor] = None
+    parts: Optional[list] = None
+
+    def leaves(self) -> list:
+        """This cache, or the caches it is made of."""
+        if self.parts is None:
+            return [self]
+        out = []
+        for p in self.parts:
+            if p is not None:
+                out += p.leaves()
+        return out
 
 
 # ----------------------------------------------------------------------------- part interfaces
@@ -188,7 +226,7 @@ class Mixer(Part):
     graph_safe = False
 
     def cache_need(self):
-        """PagedKV, FixedState or None."""
+        """PagedKV, FixedState, a CombinedNeed of several, or None."""
         return None
 
     def forward(self, x: torch.Tensor, h: torch.Tensor, ctx: StepContext, cache: Optional[LayerCache],
@@ -230,6 +268,6 @@ def role_dtype(role: str, compute_dtype: torch.dtype, stored: torch.dtype) -> to
 
 
 __all__ = [
-    "PagedKV", "FixedState", "PagedMeta", "SeqInfo", "StepContext", "LayerCache", "Part", "Norm",
+    "PagedKV", "FixedState", "CombinedNeed", "leaf_needs", "PagedMeta", "SeqInfo", "StepContext", "LayerCache", "Part", "Norm",
     "PositionEncoding", "Mixer", "FeedForward", "Block", "TensorSpec", "role_dtype",
 ]

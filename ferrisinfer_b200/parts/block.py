@@ -1,13 +1,19 @@
-"""How a layer's parts are arranged: the pre-norm residual block.
+"""How a layer's parts are arranged.
 
+The pre-norm residual block, one branch after the other:
   h += mixer(norm_1(h));  h += feed_forward(norm_2(h))
-(crates/ferrisinfer-runtime/src/reference.rs:244-249, 331-344, 362-368).  The sums are made in
-the fp32 residual stream by the last matrix product of each branch.
+(crates/ferrisinfer-runtime/src/reference.rs:244-249, 331-344, 362-368).
+
+The parallel block, both branches from the same h:
+  h += mixer(norm_1(h)) + feed_forward(norm_2(h))
+Both norms are taken before either branch adds, into buffers of their own.  A layer may have no feed-forward.
+
+The sums are made in the fp32 residual stream by the last matrix product of each branch.
 """
 
 from __future__ import annotations
 
-from .base import Block
+from .base import Block, TensorSpec
 from .plan import build_part, register_part
 
 
@@ -59,4 +65,53 @@ class PreNormResidualBlock(Block):
         self.feed_forward.forward(x, h, ctx)
 
 
+class ParallelResidualBlock(PreNormResidualBlock):
+    """h += mixer(norm_1(h)) + feed_forward(norm_2(h)); ``feed_forward`` None: the mixer's branch alone (the
+    second norm's tensor is then read if the folder has it, and not used)."""
+
+    def __init__(self, hidden_size: int, mixer, feed_forward, mixer_norm, feed_forward_norm,
+                 mixer_prefix: str = "mix", feed_forward_prefix: str = "mlp", mixer_norm_prefix: str = "norm1",
+                 feed_forward_norm_prefix: str = "norm2"):
+        super().__init__(hidden_size, mixer, feed_forward, mixer_norm, feed_forward_norm, mixer_prefix,
+                         feed_forward_prefix, mixer_norm_prefix, feed_forward_norm_prefix)
+
+    def _children(self, prefix):
+        # an empty name stands for the layer's own prefix (a mixer that names its tensors itself)
+        return [(part, f"{prefix}.{name}" if name else prefix) for part, name in zip(
+            (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward),
+            (self._names[2], self._names[0], self._names[3], self._names[1])) if part is not None]
+
+    def tensor_specs(self, prefix):
+        out = []
+        for part, p in self._children(prefix):
+            specs = part.tensor_specs(p)
+            if part is self.feed_forward_norm and self.feed_forward is None:
+                specs = [TensorSpec(s.name, s.shape, s.role, required=False) for s in specs]
+            out += specs
+        return out
+
+    def bind(self, tensors, prefix):
+        for part, p in self._children(prefix):
+            if part is self.feed_forward_norm and self.feed_forward is None:
+                continue
+            part.bind(tensors, p)
+
+    @property
+    def graph_safe(self):
+        return bool(getattr(self.mixer, "graph_safe", False)
+                    and (self.feed_forward is None or getattr(self.feed_forward, "graph_safe", False)))
+
+    def forward(self, h, ctx, cache, owns_cache):
+        T = h.shape[0]
+        x1 = ctx.workspace.get("block_normed", (T, self.hidden_size), ctx.act_dtype)
+        self.mixer_norm.forward(h, x1)
+        if self.feed_forward is not None:
+            x2 = ctx.workspace.get("block_normed_2", (T, self.hidden_size), ctx.act_dtype)
+            self.feed_forward_norm.forward(h, x2)
+        self.mixer.forward(x1, h, ctx, cache, owns_cache)
+        if self.feed_forward is not None:
+            self.feed_forward.forward(x2, h, ctx)
+
+
 register_part("block", "pre_norm_residual", PreNormResidualBlock)
+register_part("block", "parallel_residual", ParallelResidualBlock)

@@ -1,4 +1,4 @@
-"""Token embedding and the output head as parts.
+"""Token embeddings and the output head as parts.
 
 Embedding: h[t, :] = E[id_t, :], no scaling (crates/ferrisinfer-kernel/src/cpu/attention.rs:3-99).
 Output head: logits[v] = sum_k y[k] W[v, k], no bias, only for the rows asked
@@ -30,21 +30,60 @@ class TokenEmbedding(Part):
         ops.embed_gather(self.weight, token_ids, h)
 
 
+class ScaledSinusoidalEmbedding(Part):
+    """h[t, :] = E[id_t, :] * scale + pe(pos_t), with pe(p)[2i] = sin(p * base^(-2i / H)) and pe(p)[2i + 1] the cosine
+    of the same angle.  The frequencies are formed in 64-bit on the host and rounded once; angles are fp32.
+    ``needs_positions``: the model hands ``forward`` the step's positions."""
+
+    needs_positions = True
+
+    def __init__(self, vocab_size: int, hidden_size: int, scale: float = 1.0, base: float = 10000.0,
+                 weight_name: str = "weight"):
+        self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
+        self.scale, self.base, self.weight_name = float(scale), float(base), weight_name
+        self.weight = None
+        self._freq = {}
+
+    def _name(self, prefix):
+        return f"{prefix}.{self.weight_name}" if self.weight_name else prefix
+
+    def tensor_specs(self, prefix):
+        return [TensorSpec(self._name(prefix), (self.vocab_size, self.hidden_size), "embedding")]
+
+    def bind(self, tensors, prefix):
+        self.weight = tensors[self._name(prefix)]
+
+    def frequencies(self, device) -> torch.Tensor:
+        key = str(device)
+        if key not in self._freq:
+            H = self.hidden_size
+            f = [self.base ** (-2.0 * i / H) for i in range((H + 1) // 2)]
+            self._freq[key] = torch.tensor(f, dtype=torch.float64).to(torch.float32).to(device)
+        return self._freq[key]
+
+    def forward(self, token_ids, h, positions=None):
+        ops.embed_sinusoid(self.weight, token_ids, positions, self.frequencies(h.device), self.scale, h)
+
+
 class OutputHead(Part):
     """``tied_to``: tensor name of the embedding table to use as the output matrix, or None
     when the folder has a matrix of its own under ``prefix``."""
 
-    def __init__(self, vocab_size: int, hidden_size: int, tied_to=None):
+    def __init__(self, vocab_size: int, hidden_size: int, tied_to=None, weight_name: str = "weight"):
         self.vocab_size, self.hidden_size, self.tied_to = int(vocab_size), int(hidden_size), tied_to
+        self.weight_name = weight_name  # "" = the tensor is named by the prefix itself
         self.weight = None
+
+    def _name(self, prefix):
+        return f"{prefix}.{self.weight_name}" if self.weight_name else prefix
 
     def tensor_specs(self, prefix):
         if self.tied_to:
             return []
-        return [TensorSpec(f"{prefix}.weight", (self.vocab_size, self.hidden_size), "matrix")]
+        return [TensorSpec(self._name(prefix), (self.vocab_size, self.hidden_size), "matrix")]
 
     def bind(self, tensors, prefix):
-        self.weight = tensors[self.tied_to if self.tied_to else f"{prefix}.weight"]
+        self.weight = tensors[self.tied_to if self.tied_to else self._name(prefix)]
 
     def forward(self, y, logits):
         """logits fp32 [n, V] = y [n, H] W^T."""
@@ -58,4 +97,5 @@ class OutputHead(Part):
 
 
 register_part("embedding", "token_embedding", TokenEmbedding)
+register_part("embedding", "scaled_sinusoidal_embedding", ScaledSinusoidalEmbedding)
 register_part("output", "linear_head", OutputHead)

@@ -1,4 +1,4 @@
-"""The gated SiLU feed-forward (SwiGLU) as a part.
+"""Feed-forwards as parts: the gated SiLU one (SwiGLU), and a plain one with a choice of activation.
 
   u = y W_up^T;  g = y W_gate^T;  m = u * (g * sigmoid(g));  h += m W_down^T
 (crates/ferrisinfer-runtime/src/reference.rs:346-368; the reference's w1 is up_proj and w3 is
@@ -45,4 +45,43 @@ class SwiGLU(FeedForward):
         ops.gemm(act, self.down, None, h, accumulate=True)
 
 
+class DenseActivation(FeedForward):
+    """h += W_down a(W_up y), no gate, no bias.  ``activation``: "xielu" (two learned numbers p, q in the tensor
+    ``act``: softplus(p) z^2 + z / 2 for z > 0, (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2 otherwise) or "silu".
+    The activation is evaluated in fp32 on the rounded product."""
+
+    accepts_lazy_norm = True
+    graph_safe = True
+
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "xielu",
+                 up_name: str = "up", down_name: str = "down", act_name: str = "act"):
+        if activation not in ops.ACTIVATIONS:
+            raise ValueError(f"activation '{activation}' is not known ({', '.join(ops.ACTIVATIONS)})")
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.activation = activation
+        self._names = (up_name, down_name, act_name)
+        self.up = self.down = self.act = None
+
+    def tensor_specs(self, prefix):
+        H, I = self.hidden_size, self.intermediate_size
+        up, down, act = self._names
+        specs = [TensorSpec(f"{prefix}.{up}", (I, H), "matrix"), TensorSpec(f"{prefix}.{down}", (H, I), "matrix")]
+        if self.activation == "xielu":
+            specs.append(TensorSpec(f"{prefix}.{act}", (2,), "vector"))
+        return specs
+
+    def bind(self, tensors, prefix):
+        up, down, act = self._names
+        self.up, self.down = tensors[f"{prefix}.{up}"], tensors[f"{prefix}.{down}"]
+        self.act = tensors.get(f"{prefix}.{act}")
+
+    def forward(self, x, h, ctx):
+        T, I = x.shape[0], self.intermediate_size
+        z = ctx.workspace.get("ffn_act", (T, I), ctx.act_dtype)
+        ops.gemm(x, self.up, None, z)
+        ops.activation(z, z, self.activation, self.act)
+        ops.gemm(z, self.down, None, h, accumulate=True)
+
+
 register_part("feed_forward", "swiglu", SwiGLU)
+register_part("feed_forward", "dense_activation", DenseActivation)

@@ -14,6 +14,7 @@ from typing import Optional
 
 import torch
 
+from ..kernels import ops
 from .base import LayerCache, StepContext
 from .plan import LayerPlan, ModelPlan, build_part
 
@@ -30,13 +31,16 @@ class DecoderModel:
         self.final_norm = build_part("norm", plan.final_norm)
         self.output = build_part("output", plan.output)
         self.bound = False
+        # a callable (run-order index, residual stream) that sees the residual stream after every run of a layer:
+        # for tests and debugging; a model with one is stepped without graphs
+        self.after_run = None
 
     def _build_layer(self, lp: LayerPlan):
         return build_part(
             "block", lp.block,
             hidden_size=self.hidden_size,
             mixer=build_part("mixer", lp.mixer),
-            feed_forward=build_part("feed_forward", lp.feed_forward),
+            feed_forward=None if lp.feed_forward is None else build_part("feed_forward", lp.feed_forward),
             mixer_norm=build_part("norm", lp.mixer_norm),
             feed_forward_norm=build_part("norm", lp.feed_forward_norm),
         )
@@ -44,7 +48,7 @@ class DecoderModel:
     @property
     def graph_safe(self) -> bool:
         """Whether a decode step of this model may be recorded into a CUDA graph."""
-        return all(getattr(b, "graph_safe", False) for b in self.blocks)
+        return self.after_run is None and all(getattr(b, "graph_safe", False) for b in self.blocks)
 
     # ------------------------------------------------------------------ weights
     def tensor_specs(self) -> list:
@@ -90,10 +94,21 @@ class DecoderModel:
         T = ctx.num_tokens
         ctx.shared.clear()  # what parts share belongs to one pass; a context may be run again (to record a graph)
         h = ctx.workspace.get("residual", (T, self.hidden_size), torch.float32)
-        self.embedding.forward(ctx.token_ids, h)
+        if getattr(self.embedding, "needs_positions", False):
+            self.embedding.forward(ctx.token_ids, h, ctx.positions)
+        else:
+            self.embedding.forward(ctx.token_ids, h)
+        embedded = None
+        if any(step.add_embedding for step in self.plan.run_order):
+            embedded = ctx.workspace.get("embedding_output", (T, self.hidden_size), torch.float32)
+            embedded.copy_(h)
         for i, step in enumerate(self.plan.run_order):
             owner = i if step.cache_of is None else step.cache_of
+            if step.add_embedding:
+                ops.add_(h, embedded)
             self.blocks[step.layer].forward(h, ctx, caches[owner], owns_cache=step.cache_of is None)
+            if self.after_run is not None:
+                self.after_run(i, h)
         if logits_index is None or logits_index.numel() == 0:
             return None
         n = logits_index.numel()

@@ -2,6 +2,9 @@
 
   ms = sum(x^2) / H;  r = 1 / sqrt(ms + eps);  y_j = (x_j * r) * w_j
 (crates/ferrisinfer-kernel/src/cpu/reduction.rs:35-41).
+
+``GroupedRMSNorm``: the row in ``groups`` equal consecutive parts, each divided by its own root mean square; the
+weight spans the whole row.  The tensor is named by ``weight_name`` under the part's prefix ("" = the prefix itself).
 """
 
 from __future__ import annotations
@@ -30,4 +33,32 @@ class RMSNorm(Norm):
         return ops.LazyRMSNorm(h, self.weight, self.eps, out)
 
 
+class GroupedRMSNorm(Norm):
+    def __init__(self, hidden_size: int, eps: float, groups: int = 1, weight_name: str = "weight"):
+        self.hidden_size, self.eps, self.groups = int(hidden_size), float(eps), int(groups)
+        if self.groups < 1 or self.hidden_size % self.groups:
+            raise ValueError(f"{self.hidden_size} columns cannot be normed in {self.groups} equal groups")
+        self.weight_name = weight_name
+        self.weight = None
+
+    def _name(self, prefix):
+        return f"{prefix}.{self.weight_name}" if self.weight_name else prefix
+
+    def tensor_specs(self, prefix):
+        return [TensorSpec(self._name(prefix), (self.hidden_size,), "norm")]
+
+    def bind(self, tensors, prefix):
+        self.weight = tensors[self._name(prefix)]
+
+    def forward(self, h, out, row_index=None):
+        ops.grouped_rmsnorm(h, self.weight, self.eps, self.groups, out, row_index)
+
+    def lazy(self, h, out):
+        if self.groups == 1:
+            return ops.LazyRMSNorm(h, self.weight, self.eps, out)
+        self.forward(h, out)
+        return out
+
+
 register_part("norm", "rmsnorm", RMSNorm)
+register_part("norm", "grouped_rmsnorm", GroupedRMSNorm)

@@ -46,11 +46,12 @@ class TensorSpec:
 
 @dataclass(frozen=True)
 class LayerPlan:
-    """One layer: a block kind wiring two norms, a mixer and a feed-forward."""
+    """One layer: a block kind wiring two norms, a mixer and a feed-forward (None: the layer has none, where
+    its block kind allows that)."""
 
     prefix: str  # tensor-name prefix, e.g. "model.layers.3"
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]
     mixer_norm: PartSpec
     feed_forward_norm: PartSpec
     block: PartSpec = PartSpec("pre_norm_residual")
@@ -62,11 +63,14 @@ class RunStep:
 
     ``layer``: index into ``ModelPlan.layers``.  ``cache_of``: None = this run
     has a cache of its own; an int = the index of an EARLIER run-order entry
-    whose cache this run reads without writing.
+    whose cache this run reads without writing.  ``add_embedding``: the embedding's output (the residual
+    stream as it was before the first run) is added to the residual stream right before this run, as a
+    model that loops over some of its layers does at the start of every repeat.
     """
 
     layer: int
     cache_of: Optional[int] = None
+    add_embedding: bool = False
 
 
 @dataclass(frozen=True)

@@ -9,6 +9,9 @@ rotary_dim).  The angle ``float(pos) * inv_freq[i]`` and its sine and cosine
 are fp32, formed in the kernel that also writes the cache.
 
 ``NoPosition``: nothing is encoded (the keys go to the cache as they are).
+
+``DistanceSlopes``: nothing is rotated; the score of the key at position j for the query at position P loses
+slope_h * (P - j), with slope_h = 2^(-span (h + 1) / heads) for head h = 0 .. heads - 1 (span 8 by default).
 """
 
 from __future__ import annotations
@@ -71,5 +74,25 @@ class NoPosition(PositionEncoding):
         return None, 0
 
 
+class DistanceSlopes(PositionEncoding):
+    graph_safe = True
+
+    def __init__(self, span: float = 8.0):
+        self.span = float(span)
+        self._device = {}
+
+    def rotary_table(self, device=None):
+        return None, 0
+
+    def score_slopes(self, num_heads, device=None):
+        device = torch.device(device if device is not None else "cuda")
+        key = (str(device), int(num_heads))
+        if key not in self._device:
+            slopes = [2.0 ** (-self.span * (h + 1) / num_heads) for h in range(num_heads)]
+            self._device[key] = torch.tensor(slopes, dtype=torch.float64).to(torch.float32).to(device)
+        return self._device[key]
+
+
 register_part("position", "rotary", RotaryEncoding)
+register_part("position", "distance_slopes", DistanceSlopes)
 register_part("position", "none", NoPosition)
