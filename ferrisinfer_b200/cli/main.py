@@ -133,9 +133,12 @@ def _run(cmd, args, ns, out) -> int:
         for i, step in enumerate(plan.run_order):
             lp = plan.layers[step.layer]
             reads = "" if step.cache_of is None else f" (reads the cache of run {step.cache_of})"
-            print(f"run {i}: layer {step.layer}{reads}: {lp.mixer_norm.kind} -> {lp.mixer.kind} "
-                  f"{ {k: v for k, v in lp.mixer.params.items() if k != 'position'} } -> {lp.feed_forward_norm.kind} "
-                  f"-> {lp.feed_forward.kind} {lp.feed_forward.params}", file=out)
+            if step.add_embedding:
+                reads += " (the embedding output is added first)"
+            ff = "no feed-forward" if lp.feed_forward is None else \
+                f"{lp.feed_forward_norm.kind} -> {lp.feed_forward.kind} {lp.feed_forward.params}"
+            print(f"run {i}: layer {step.layer} [{lp.block.kind}]{reads}: {lp.mixer_norm.kind} -> {lp.mixer.kind} "
+                  f"{ {k: v for k, v in lp.mixer.params.items() if k != 'position'} } -> {ff}", file=out)
         print(f"final norm: {plan.final_norm.kind}; output: {plan.output.kind} {plan.output.params}", file=out)
         return 0
 
