@@ -398,6 +398,53 @@ __global__ void __launch_bounds__(256) grouped_rmsnorm_kernel(const float* x, co
     for (int i = lane; i < n; i += 32) o[i] = from_float<TOut>((xr[i] * inv) * wg[i]);
 }
 
+// Two such norms of the same rows with weights of their own (the two branches of a parallel block), in one launch.
+template <typename TOut>
+__global__ void __launch_bounds__(256) grouped_rmsnorm_pair_kernel(const float* x, const float* __restrict__ w1,
+                                                                   const float* __restrict__ w2, TOut* __restrict__ out1,
+                                                                   TOut* __restrict__ out2, int rows, int hidden,
+                                                                   int groups, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (item >= (long long)rows * groups) return;
+    const int r = (int)(item / groups), g = (int)(item % groups);
+    const int n = hidden / groups;
+    const size_t at = (size_t)r * hidden + (size_t)g * n;
+    const float* xr = x + at;
+    float ss = 0.0f;
+    for (int i = lane; i < n; i += 32) {
+        const float v = xr[i];
+        ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)n + eps);
+    const float* a = w1 + (size_t)g * n;
+    const float* b = w2 + (size_t)g * n;
+    for (int i = lane; i < n; i += 32) {
+        const float v = xr[i] * inv;
+        out1[at + i] = from_float<TOut>(v * a[i]);
+        out2[at + i] = from_float<TOut>(v * b[i]);
+    }
+}
+
+FERRIS_API int ferris_grouped_rmsnorm_pair(const float* x, const float* w1, const float* w2, void* out1, void* out2,
+                                           int out_dtype, int rows, int hidden, int groups, float eps, void* stream) {
+    if (rows <= 0) return FERRIS_OK;
+    if (hidden <= 0 || groups <= 0 || hidden % groups) FERRIS_REFUSE("grouped rmsnorm: %d columns in %d groups", hidden, groups);
+    const long long items = (long long)rows * groups;
+    const dim3 grid((unsigned)((items + 7) / 8)), block(256);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == FERRIS_F32)
+        ferris_launch(grouped_rmsnorm_pair_kernel<float>, grid, block, 0, s, x, w1, w2, (float*)out1, (float*)out2, rows, hidden, groups, eps);
+    else if (out_dtype == FERRIS_BF16)
+        ferris_launch(grouped_rmsnorm_pair_kernel<bf16>, grid, block, 0, s, x, w1, w2, (bf16*)out1, (bf16*)out2, rows, hidden, groups, eps);
+    else
+        FERRIS_REFUSE("grouped rmsnorm: unknown dtype %d", out_dtype);
+    FERRIS_LAUNCH_CHECK();
+}
+
 FERRIS_API int ferris_grouped_rmsnorm(const float* x, const float* w, const int* row_index, void* out, int out_dtype,
                                       int rows, int hidden, int groups, float eps, void* stream) {
     if (rows <= 0) return FERRIS_OK;

@@ -7,7 +7,8 @@
 // The columns of S do not depend on one another, so a warp owns eight of them for one (request, head) and walks
 // the request's tokens of the step in order: a lane holds rows lane, lane + 32, ... of its eight columns in
 // registers, updates them with fp32 FMAs, and the eight dot products with q are summed over the warp.  No barrier,
-// no shared memory; a step of single tokens and a long portion of a prompt are the same loop.  The state lies
+// no shared memory; a step of single tokens and a portion of a prompt are the same loop, and a long portion is cut
+// into segments that run side by side (see the kernel).  The state lies
 // transposed in memory, [slot, head, vdim, dim], so that a warp reads and writes whole rows of it.
 // q, k, v may be passed through SiLU on the way in (`silu`), in fp32 whatever the storage type.
 #include <math.h>
@@ -21,39 +22,86 @@ constexpr int LA_WARPS = 4;
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
 
-template <typename T, int RPL>  // RPL rows of the state per lane: dim <= 32 * RPL
+// Eight sums over the warp's lanes with nine shuffles instead of forty: at each of the first three steps a lane
+// hands half of its partial sums to its partner and keeps the other half.  Every lane returns the sum of column
+// ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1); the order of the additions is fixed.
+__device__ __forceinline__ float reduce_columns(const float (&o)[LA_COLS], int lane) {
+    const unsigned full = 0xffffffffu;
+    const bool h1 = lane & 16, h2 = lane & 8, h3 = lane & 4;
+    float a[4], b[2];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        const float send = h1 ? o[c] : o[c + 4], keep = h1 ? o[c + 4] : o[c];
+        a[c] = keep + __shfl_xor_sync(full, send, 16);
+    }
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        const float send = h2 ? a[c] : a[c + 2], keep = h2 ? a[c + 2] : a[c];
+        b[c] = keep + __shfl_xor_sync(full, send, 8);
+    }
+    const float send = h3 ? b[0] : b[1], keep = h3 ? b[1] : b[0];
+    float r = keep + __shfl_xor_sync(full, send, 4);
+    r += __shfl_xor_sync(full, r, 2);
+    r += __shfl_xor_sync(full, r, 1);
+    return r;
+}
+
+// Long portions of prompts are cut into segments of `seg_len` tokens that run side by side (the recurrence is linear
+// in the state): MODE 1 sums each segment's own k v^T from a zero state into `scratch`; the combine kernel below turns
+// those into the state at each segment's start; MODE 2 then runs each segment from that state and writes the outputs,
+// the last segment of a request also the request's state.  MODE 0 is the whole request in one go, from and to its slot
+// (single tokens and short portions).  A segment's place in `scratch` is (its first row / seg_len) + its request's
+// index in the step, which no two segments share.
+template <typename T, int RPL, int MODE>  // RPL rows of the state per lane: dim <= 32 * RPL
 __global__ void __launch_bounds__(LA_WARPS * 32) linear_attention_scan_kernel(
     const T* qkv, int ld, int q_off, int k_off, int v_off, float* __restrict__ out, int ldo, float* state,
-    const float* __restrict__ decay, const int* __restrict__ seq_q_start, const int* __restrict__ seq_state_slot,
-    int heads, int dim, int vdim, int silu, int write_state) {
+    float* scratch, const float* __restrict__ decay, const int* __restrict__ seq_q_start,
+    const int* __restrict__ seq_state_slot, int heads, int dim, int vdim, int silu, int write_state, int seg_len,
+    int segs_max) {
     pdl_wait();
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int h = blockIdx.y, seq = blockIdx.z;
-    const int col0 = (blockIdx.x * LA_WARPS + warp) * LA_COLS;
+    const int h = blockIdx.y;
+    const int seq = MODE == 0 ? blockIdx.x : blockIdx.x / segs_max;
+    const int seg = MODE == 0 ? 0 : blockIdx.x % segs_max;
+    const int col0 = (blockIdx.z * LA_WARPS + warp) * LA_COLS;
     if (col0 >= vdim) return;
-    const int row0 = seq_q_start[seq], row1 = seq_q_start[seq + 1];
-    if (row1 <= row0) return;
+    int row0 = seq_q_start[seq];
+    int row1 = seq_q_start[seq + 1];
+    bool last = true;
+    if (MODE != 0) {
+        row0 += seg * seg_len;
+        if (row0 >= row1) return;
+        last = row0 + seg_len >= row1;
+        if (!last) row1 = row0 + seg_len;
+        if (MODE == 1 && last) return;  // nobody starts from the end of the last segment
+    }
     const float lam = decay[h];
-    float* st = state + (((size_t)seq_state_slot[seq] * heads + h) * vdim + col0) * dim;
+    const size_t tile = ((size_t)h * vdim + col0) * dim;
+    const size_t per_state = (size_t)heads * vdim * dim;
+    float* slot_state = state + (size_t)seq_state_slot[seq] * per_state + tile;
+    float* seg_state = MODE == 0 ? slot_state : scratch + (size_t)(row0 / seg_len + seq) * per_state + tile;
     float S[LA_COLS][RPL];
 #pragma unroll
     for (int c = 0; c < LA_COLS; ++c)
 #pragma unroll
         for (int r = 0; r < RPL; ++r) {
             const int i = lane + 32 * r;
-            S[c][r] = (col0 + c < vdim && i < dim) ? st[(size_t)c * dim + i] : 0.0f;
+            S[c][r] = (MODE != 1 && col0 + c < vdim && i < dim) ? seg_state[(size_t)c * dim + i] : 0.0f;
         }
+    const int my_col = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
     for (int t = row0; t < row1; ++t) {
         const T* row = qkv + (size_t)t * ld;
         float kk[RPL], qq[RPL], vv[LA_COLS];
 #pragma unroll
         for (int r = 0; r < RPL; ++r) {
             const int i = lane + 32 * r;
-            float a = i < dim ? to_float(row[k_off + h * dim + i]) : 0.0f;
-            float b = i < dim ? to_float(row[q_off + h * dim + i]) : 0.0f;
+            const float a = i < dim ? to_float(row[k_off + h * dim + i]) : 0.0f;
             kk[r] = silu ? silu_f(a) : a;
-            qq[r] = silu ? silu_f(b) : b;
+            if (MODE != 1) {
+                const float b = i < dim ? to_float(row[q_off + h * dim + i]) : 0.0f;
+                qq[r] = silu ? silu_f(b) : b;
+            }
         }
 #pragma unroll
         for (int c = 0; c < LA_COLS; ++c) {
@@ -67,24 +115,51 @@ __global__ void __launch_bounds__(LA_WARPS * 32) linear_attention_scan_kernel(
 #pragma unroll
             for (int r = 0; r < RPL; ++r) {
                 S[c][r] = fmaf(kk[r], vv[c], lam * S[c][r]);
-                acc = fmaf(S[c][r], qq[r], acc);
+                if (MODE != 1) acc = fmaf(S[c][r], qq[r], acc);
             }
-            o[c] = warp_sum(acc);
+            o[c] = acc;
         }
-        float mine = 0.0f;
-#pragma unroll
-        for (int c = 0; c < LA_COLS; ++c)
-            if (lane == c) mine = o[c];
-        if (lane < LA_COLS && col0 + lane < vdim) out[(size_t)t * ldo + h * vdim + col0 + lane] = mine;
+        if (MODE != 1) {
+            const float mine = reduce_columns(o, lane);
+            if ((lane & 3) == 0 && col0 + my_col < vdim) out[(size_t)t * ldo + h * vdim + col0 + my_col] = mine;
+        }
     }
-    if (write_state) {
+    float* dst = MODE == 1 ? seg_state : slot_state;
+    if (MODE == 1 || (write_state && last)) {
 #pragma unroll
         for (int c = 0; c < LA_COLS; ++c)
 #pragma unroll
             for (int r = 0; r < RPL; ++r) {
                 const int i = lane + 32 * r;
-                if (col0 + c < vdim && i < dim) st[(size_t)c * dim + i] = S[c][r];
+                if (col0 + c < vdim && i < dim) dst[(size_t)c * dim + i] = S[c][r];
             }
+    }
+}
+
+// Between the two passes over segments: scratch holds each full segment's own sum; afterwards it holds the state at
+// each segment's start, S_start(0) = the request's state, S_start(s + 1) = decay^seg_len S_start(s) + sum(s).
+__global__ void __launch_bounds__(256) linear_attention_combine_kernel(
+    const float* state, float* scratch, const float* __restrict__ decay, const int* __restrict__ seq_q_start,
+    const int* __restrict__ seq_state_slot, int heads, int dim, int vdim, int seg_len) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int seq = blockIdx.y;
+    const size_t per_state = (size_t)heads * vdim * dim;
+    const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= per_state) return;
+    const int row0 = seq_q_start[seq], row1 = seq_q_start[seq + 1];
+    if (row1 <= row0) return;
+    const int h = (int)(e / ((size_t)vdim * dim));
+    const float lam = decay[h];
+    float step = 1.0f;
+    for (int i = 0; i < seg_len; ++i) step *= lam;  // the factor a state takes over one full segment
+    float S = state[(size_t)seq_state_slot[seq] * per_state + e];
+    for (int r = row0; r < row1; r += seg_len) {
+        float* at = scratch + (size_t)(r / seg_len + seq) * per_state + e;
+        const bool full = r + seg_len < row1;
+        const float own = full ? *at : 0.0f;
+        *at = S;
+        S = fmaf(step, S, own);
     }
 }
 
@@ -114,14 +189,16 @@ __global__ void __launch_bounds__(256) gated_rmsnorm_kernel(const float* o, int 
     }
 }
 
-template <typename T>
-int launch_scan(const void* qkv, int ld, int q_off, int k_off, int v_off, float* out, int ldo, float* state,
-                const float* decay, const int* seq_q_start, const int* seq_state_slot, int seqs, int heads, int dim,
-                int vdim, int silu, int write_state, cudaStream_t s) {
-    const dim3 grid((vdim + LA_COLS * LA_WARPS - 1) / (LA_COLS * LA_WARPS), heads, seqs), block(LA_WARPS * 32);
-#define FERRIS_LA_LAUNCH(RPL)                                                                                          \
-    ferris_launch(linear_attention_scan_kernel<T, RPL>, grid, block, 0, s, (const T*)qkv, ld, q_off, k_off, v_off, out, \
-                  ldo, state, decay, seq_q_start, seq_state_slot, heads, dim, vdim, silu, write_state)
+template <typename T, int MODE>
+void launch_scan_mode(const void* qkv, int ld, int q_off, int k_off, int v_off, float* out, int ldo, float* state,
+                      float* scratch, const float* decay, const int* seq_q_start, const int* seq_state_slot, int seqs,
+                      int heads, int dim, int vdim, int silu, int write_state, int seg_len, int segs_max, cudaStream_t s) {
+    const dim3 grid(MODE == 0 ? seqs : seqs * segs_max, heads, (vdim + LA_COLS * LA_WARPS - 1) / (LA_COLS * LA_WARPS));
+    const dim3 block(LA_WARPS * 32);
+#define FERRIS_LA_LAUNCH(RPL)                                                                                       \
+    ferris_launch(linear_attention_scan_kernel<T, RPL, MODE>, grid, block, 0, s, (const T*)qkv, ld, q_off, k_off,   \
+                  v_off, out, ldo, state, scratch, decay, seq_q_start, seq_state_slot, heads, dim, vdim, silu,       \
+                  write_state, seg_len, segs_max)
     if (dim <= 32)
         FERRIS_LA_LAUNCH(1);
     else if (dim <= 64)
@@ -131,6 +208,24 @@ int launch_scan(const void* qkv, int ld, int q_off, int k_off, int v_off, float*
     else
         FERRIS_LA_LAUNCH(8);
 #undef FERRIS_LA_LAUNCH
+}
+
+template <typename T>
+int launch_scan(const void* qkv, int ld, int q_off, int k_off, int v_off, float* out, int ldo, float* state,
+                float* scratch, const float* decay, const int* seq_q_start, const int* seq_state_slot, int seqs,
+                int heads, int dim, int vdim, int silu, int write_state, int seg_len, int segs_max, cudaStream_t s) {
+    if (segs_max <= 1) {
+        launch_scan_mode<T, 0>(qkv, ld, q_off, k_off, v_off, out, ldo, state, scratch, decay, seq_q_start, seq_state_slot,
+                               seqs, heads, dim, vdim, silu, write_state, seg_len, 1, s);
+        FERRIS_LAUNCH_CHECK();
+    }
+    launch_scan_mode<T, 1>(qkv, ld, q_off, k_off, v_off, out, ldo, state, scratch, decay, seq_q_start, seq_state_slot, seqs,
+                           heads, dim, vdim, silu, write_state, seg_len, segs_max, s);
+    const size_t per_state = (size_t)heads * vdim * dim;
+    ferris_launch(linear_attention_combine_kernel, dim3((unsigned)((per_state + 255) / 256), seqs), dim3(256), 0, s,
+                  (const float*)state, scratch, decay, seq_q_start, seq_state_slot, heads, dim, vdim, seg_len);
+    launch_scan_mode<T, 2>(qkv, ld, q_off, k_off, v_off, out, ldo, state, scratch, decay, seq_q_start, seq_state_slot, seqs,
+                           heads, dim, vdim, silu, write_state, seg_len, segs_max, s);
     FERRIS_LAUNCH_CHECK();
 }
 
@@ -139,19 +234,23 @@ int launch_scan(const void* qkv, int ld, int q_off, int k_off, int v_off, float*
 // qkv: rows of ld elements holding q heads at q_off, k heads at k_off (heads x dim each) and v heads at v_off
 // (heads x vdim), head by head; out: fp32 [tokens, heads x vdim] rows ldo apart; state: fp32 [slots, heads, vdim, dim];
 // decay: fp32 [heads].  The rows of request s are seq_q_start[s] .. seq_q_start[s + 1] - 1, in order.
+// segs_max > 1: no request brings more than segs_max * seg_len tokens, and they run as segments of seg_len side by
+// side through `scratch`, fp32 [tokens / seg_len + seqs + 1, heads, vdim, dim].
 FERRIS_API int ferris_linear_attention(const void* qkv, int ld, int q_off, int k_off, int v_off, int dtype, float* out,
                                        int ldo, float* state, const float* decay, const int* seq_q_start,
                                        const int* seq_state_slot, int seqs, int heads, int dim, int vdim, int silu,
-                                       int write_state, void* stream) {
+                                       int write_state, int seg_len, int segs_max, float* scratch, void* stream) {
     if (seqs <= 0) return FERRIS_OK;
+    if (segs_max > 1 && (!scratch || seg_len <= 0)) FERRIS_REFUSE("linear attention: segments need scratch and a length");
+    if (seqs > 65535) FERRIS_REFUSE("linear attention: %d requests are more than one launch takes", seqs);
     if (heads <= 0 || dim <= 0 || vdim <= 0 || dim > 256) FERRIS_REFUSE("linear attention: heads=%d dim=%d vdim=%d (dim at most 256)", heads, dim, vdim);
-    if (heads > 65535 || seqs > 65535) FERRIS_REFUSE("linear attention: %d heads of %d requests are more than one launch takes", heads, seqs);
+    if (heads > 65535) FERRIS_REFUSE("linear attention: %d heads are more than one launch takes", heads);
     if (!state || !decay) FERRIS_REFUSE("linear attention: no state or no decay");
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == FERRIS_F32)
-        return launch_scan<float>(qkv, ld, q_off, k_off, v_off, out, ldo, state, decay, seq_q_start, seq_state_slot, seqs, heads, dim, vdim, silu, write_state, s);
+        return launch_scan<float>(qkv, ld, q_off, k_off, v_off, out, ldo, state, scratch, decay, seq_q_start, seq_state_slot, seqs, heads, dim, vdim, silu, write_state, seg_len, segs_max, s);
     if (dtype == FERRIS_BF16)
-        return launch_scan<bf16>(qkv, ld, q_off, k_off, v_off, out, ldo, state, decay, seq_q_start, seq_state_slot, seqs, heads, dim, vdim, silu, write_state, s);
+        return launch_scan<bf16>(qkv, ld, q_off, k_off, v_off, out, ldo, state, scratch, decay, seq_q_start, seq_state_slot, seqs, heads, dim, vdim, silu, write_state, seg_len, segs_max, s);
     FERRIS_REFUSE("linear attention: unknown dtype %d", dtype);
 }
 

@@ -7,7 +7,9 @@
 // back before the step takes it from the state, otherwise from the step's own rows.  `advance` then moves the
 // state on, one thread per (request, channel) walking the taps - 1 places in ascending order (with fewer new
 // tokens than places, a place takes the value of a later place, which that thread has not overwritten yet).
-// In one launch, a block that advanced the state could overtake a block that still reads it.
+// In one launch, a block that advanced the state could overtake a block that still reads it.  A step in which every
+// request brings ONE token needs neither: one thread per (request, channel) reads the state, forms the output and
+// shifts the state by one place, in one launch.
 #include "common.cuh"
 
 namespace {
@@ -66,6 +68,33 @@ __global__ void __launch_bounds__(256) short_conv_advance_kernel(const T* y, int
     }
 }
 
+template <typename T>
+__global__ void __launch_bounds__(256) short_conv_single_kernel(const T* y, int ldy, T* __restrict__ out, int ldo,
+                                                                const float* __restrict__ w, float* state,
+                                                                const int* __restrict__ positions,
+                                                                const int* __restrict__ seq_state_slot, int channels,
+                                                                int taps) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t = blockIdx.x;  // the request's only row of the step
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= channels) return;
+    const int n = taps - 1;
+    const int pos = positions[t];
+    float* st = state + (size_t)seq_state_slot[t] * n * channels + c;
+    const float* wc = w + (size_t)c * taps;
+    const float own = to_float(y[(size_t)t * ldy + c]);
+    float acc = own;
+    for (int j = 0; j < n; ++j) {  // place j of the state is the input n - j positions back
+        const float v = st[(size_t)j * channels];
+        if (j > 0) st[(size_t)(j - 1) * channels] = v;
+        acc = fmaf(wc[j], pos - (n - j) >= 0 ? v : 0.0f, acc);
+    }
+    acc = fmaf(wc[n], own, acc);
+    if (n > 0) st[(size_t)(n - 1) * channels] = own;
+    out[(size_t)t * ldo + c] = from_float<T>(acc);
+}
+
 }  // namespace
 
 // y, out: [tokens, channels] rows ldy / ldo apart (out must not be y); w: fp32 [channels, taps];
@@ -73,7 +102,7 @@ __global__ void __launch_bounds__(256) short_conv_advance_kernel(const T* y, int
 FERRIS_API int ferris_short_conv(const void* y, int ldy, void* out, int ldo, int dtype, const float* w, float* state,
                                  const int* token_seq, const int* positions, const int* seq_q_start,
                                  const int* seq_start_pos, const int* seq_state_slot, int tokens, int seqs, int channels,
-                                 int taps, int advance, void* stream) {
+                                 int taps, int advance, int single_tokens, void* stream) {
     if (tokens <= 0 || seqs <= 0) return FERRIS_OK;
     if (channels <= 0 || taps <= 0) FERRIS_REFUSE("short conv: channels=%d taps=%d", channels, taps);
     if (taps > 1 && !state) FERRIS_REFUSE("short conv: %d taps need a state", taps);
@@ -83,6 +112,16 @@ FERRIS_API int ferris_short_conv(const void* y, int ldy, void* out, int ldo, int
     const int tiles = (channels + threads - 1) / threads;
     if (tiles > 65535) FERRIS_REFUSE("short conv: %d channels are more than one launch takes", channels);
     const dim3 block(threads), grid_a(tokens, tiles), grid_b(seqs, tiles);
+    if (single_tokens && advance && tokens == seqs && dtype == FERRIS_F32) {
+        ferris_launch(short_conv_single_kernel<float>, grid_a, block, 0, s, (const float*)y, ldy, (float*)out, ldo, w, state,
+                      positions, seq_state_slot, channels, taps);
+        FERRIS_LAUNCH_CHECK();
+    }
+    if (single_tokens && advance && tokens == seqs && dtype == FERRIS_BF16) {
+        ferris_launch(short_conv_single_kernel<bf16>, grid_a, block, 0, s, (const bf16*)y, ldy, (bf16*)out, ldo, w, state,
+                      positions, seq_state_slot, channels, taps);
+        FERRIS_LAUNCH_CHECK();
+    }
     if (dtype == FERRIS_F32) {
         ferris_launch(short_conv_apply_kernel<float>, grid_a, block, 0, s, (const float*)y, ldy, (float*)out, ldo, w,
                       (const float*)state, token_seq, positions, seq_start_pos, seq_state_slot, channels, taps);

@@ -727,6 +727,27 @@ def grouped_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, groups: i
     )
 
 
+def grouped_rmsnorm_pair(x: torch.Tensor, weight1: torch.Tensor, weight2: torch.Tensor, eps: float, groups: int,
+                         out1: torch.Tensor, out2: torch.Tensor):
+    """Two grouped RMSNorms of the same rows, with weights and outputs of their own, in one launch."""
+    _need(x, "rmsnorm input", torch.float32)
+    _need(weight1, "rmsnorm weight", torch.float32)
+    _need(weight2, "rmsnorm weight", torch.float32)
+    _need(out1, "rmsnorm output")
+    _need(out2, "rmsnorm output", out1.dtype)
+    rows, H = out1.shape
+    if (x.shape != (rows, H) or out2.shape != (rows, H) or weight1.numel() != H or weight2.numel() != H or groups < 1
+            or H % groups):
+        raise KernelError(f"grouped rmsnorm pair: x {tuple(x.shape)}, outputs {tuple(out1.shape)} {tuple(out2.shape)}, "
+                          f"{groups} groups")
+    _check(
+        _lib().ferris_grouped_rmsnorm_pair(_ptr(x), _ptr(weight1), _ptr(weight2), _ptr(out1), _ptr(out2),
+                                           _c_int(_dt(out1, "rmsnorm output")), _c_int(rows), _c_int(H), _c_int(groups),
+                                           _c_float(eps), _stream()),
+        "grouped rmsnorm pair",
+    )
+
+
 def add_(h: torch.Tensor, x: torch.Tensor):
     """h += x, both fp32 and of one shape."""
     _need(h, "sum", torch.float32)
@@ -803,22 +824,30 @@ def short_conv(y: torch.Tensor, out: torch.Tensor, weight: torch.Tensor, state: 
         _need(state, "convolution state", torch.float32)
         if state.shape[1:] != (taps - 1, C):
             raise KernelError(f"short conv: state {tuple(state.shape)} for {taps} taps of {C} channels")
-    kernels = 2 if (advance and taps > 1) else 1
+    single = bool(advance and getattr(ctx, "max_q_len", 0) == 1 and T == ctx.num_seqs)  # one token each: one launch
+    kernels = 2 if (advance and taps > 1 and not single) else 1
     _check(
         _lib().ferris_short_conv(_ptr(y), _c_int(ldy), _ptr(out), _c_int(ldo), _c_int(_dt(y, "short conv")), _ptr(weight),
                                  _ptr(state if taps > 1 else None), _ptr(ctx.token_seq), _ptr(ctx.positions),
                                  _ptr(ctx.seq_q_start), _ptr(ctx.seq_start_pos), _ptr(ctx.seq_state_slot), _c_int(T),
-                                 _c_int(ctx.num_seqs), _c_int(C), _c_int(taps), _c_int(1 if advance else 0), _stream()),
+                                 _c_int(ctx.num_seqs), _c_int(C), _c_int(taps), _c_int(1 if advance else 0),
+                                 _c_int(1 if single else 0), _stream()),
         "short conv", kernels,
     )
 
 
+LINEAR_ATTENTION_SEGMENT = 128
+
+
 def linear_attention(qkv: torch.Tensor, offsets: tuple, out: torch.Tensor, state: torch.Tensor, decay: torch.Tensor,
-                     ctx, heads: int, dim: int, vdim: int, silu: bool = False, write_state: bool = True):
+                     ctx, heads: int, dim: int, vdim: int, silu: bool = False, write_state: bool = True,
+                     segment: Optional[int] = None):
     """Decayed linear attention of the step's tokens, request by request from each request's state:
     S <- decay[h] S + k v^T, o = S^T q per head.  ``qkv`` rows hold q, k heads (heads x dim) and v heads
     (heads x vdim) at the column ``offsets`` (q, k, v); ``out`` fp32 [T, heads x vdim]; ``state`` fp32
-    [slots, heads, vdim, dim].  ``silu``: q, k and v pass through SiLU on the way in."""
+    [slots, heads, vdim, dim].  ``silu``: q, k and v pass through SiLU on the way in.  A request that brings more
+    than ``segment`` tokens (128 by default) runs as segments side by side: a pass that sums each segment alone, one
+    that carries the state from segment to segment, one that forms the outputs (scratch from the step's workspace)."""
     T, width, ld = _rows(qkv, "linear attention input")
     T2, n, ldo = _rows(out, "linear attention output")
     _need(state, "linear attention state", torch.float32)
@@ -827,13 +856,23 @@ def linear_attention(qkv: torch.Tensor, offsets: tuple, out: torch.Tensor, state
     if (T2 != T or out.dtype != torch.float32 or n != heads * vdim or state.shape[1:] != (heads, vdim, dim)
             or decay.numel() != heads or max(q_off, k_off) + heads * dim > width or v_off + heads * vdim > width):
         raise KernelError(f"linear attention: qkv {tuple(qkv.shape)}, out {tuple(out.shape)}, state {tuple(state.shape)}")
+    seg = int(segment or LINEAR_ATTENTION_SEGMENT)
+    longest = int(getattr(ctx, "max_q_len", 0) or T)
+    segs_max = max(1, -(-longest // seg))
+    scratch = None
+    if segs_max > 1:
+        floats = (T // seg + ctx.num_seqs + 1) * heads * vdim * dim
+        ws = getattr(ctx, "workspace", None)
+        scratch = ws.get("linear_attn_segments", (floats,), torch.float32) if ws is not None else \
+            torch.empty(floats, dtype=torch.float32, device=qkv.device)
     _check(
         _lib().ferris_linear_attention(_ptr(qkv), _c_int(ld), _c_int(q_off), _c_int(k_off), _c_int(v_off),
                                        _c_int(_dt(qkv, "linear attention")), _ptr(out), _c_int(ldo), _ptr(state),
                                        _ptr(decay), _ptr(ctx.seq_q_start), _ptr(ctx.seq_state_slot), _c_int(ctx.num_seqs),
                                        _c_int(heads), _c_int(dim), _c_int(vdim), _c_int(1 if silu else 0),
-                                       _c_int(1 if write_state else 0), _stream()),
-        "linear attention",
+                                       _c_int(1 if write_state else 0), _c_int(seg), _c_int(segs_max), _ptr(scratch),
+                                       _stream()),
+        "linear attention", 1 if segs_max == 1 else 3,
     )
 
 

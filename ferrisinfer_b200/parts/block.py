@@ -104,10 +104,14 @@ class ParallelResidualBlock(PreNormResidualBlock):
     def forward(self, h, ctx, cache, owns_cache):
         T = h.shape[0]
         x1 = ctx.workspace.get("block_normed", (T, self.hidden_size), ctx.act_dtype)
-        self.mixer_norm.forward(h, x1)
-        if self.feed_forward is not None:
+        if self.feed_forward is None:
+            self.mixer_norm.forward(h, x1)
+        else:
             x2 = ctx.workspace.get("block_normed_2", (T, self.hidden_size), ctx.act_dtype)
-            self.feed_forward_norm.forward(h, x2)
+            pair = getattr(self.mixer_norm, "forward_pair", None)
+            if pair is None or not pair(self.feed_forward_norm, h, x1, x2):  # both norms in one launch where they can be
+                self.mixer_norm.forward(h, x1)
+                self.feed_forward_norm.forward(h, x2)
         self.mixer.forward(x1, h, ctx, cache, owns_cache)
         if self.feed_forward is not None:
             self.feed_forward.forward(x2, h, ctx)

@@ -59,6 +59,15 @@ class GroupedRMSNorm(Norm):
         self.forward(h, out)
         return out
 
+    def forward_pair(self, other, h, out, other_out) -> bool:
+        """This norm and ``other`` of the same rows in one launch; False (nothing done) if ``other`` is not the same
+        norm with another weight."""
+        if not isinstance(other, GroupedRMSNorm) or (other.hidden_size, other.eps, other.groups) != (
+                self.hidden_size, self.eps, self.groups):
+            return False
+        ops.grouped_rmsnorm_pair(h, self.weight, other.weight, self.eps, self.groups, out, other_out)
+        return True
+
 
 register_part("norm", "rmsnorm", RMSNorm)
 register_part("norm", "grouped_rmsnorm", GroupedRMSNorm)

@@ -74,7 +74,8 @@ def fake_ctx(device, q_lens, start_pos, slots):
     token_seq = [s for s in range(S) for _ in range(q_lens[s])]
     positions = [start_pos[s] + i for s in range(S) for i in range(q_lens[s])]
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=device)
-    return SimpleNamespace(num_tokens=q_start[-1], num_seqs=S, token_seq=i32(token_seq), positions=i32(positions),
+    return SimpleNamespace(num_tokens=q_start[-1], num_seqs=S, max_q_len=max(q_lens), workspace=None,
+                           token_seq=i32(token_seq), positions=i32(positions),
                            seq_q_start=i32(q_start), seq_start_pos=i32(start_pos), seq_state_slot=i32(slots))
 
 
@@ -89,6 +90,12 @@ def test_grouped_rmsnorm(device, hidden, groups):
     out = torch.empty(9, hidden, device=device)
     ops.grouped_rmsnorm(x, w, 1e-5, groups, out)
     assert torch.allclose(out.cpu().double(), want, atol=1e-5, rtol=1e-5)
+    w2 = 1 + 0.2 * torch.randn(hidden, device=device)
+    one, two = torch.empty_like(out), torch.empty_like(out)
+    ops.grouped_rmsnorm_pair(x, w, w2, 1e-5, groups, one, two)  # both branches' norms in one launch
+    assert torch.allclose(one, out, atol=1e-6, rtol=1e-6)  # (one group: the plain kernel sums in another order)
+    assert torch.allclose(two.cpu().double(), plain.grouped_rms_norm(x.double().cpu(), w2.double().cpu(), groups, 1e-5),
+                          atol=1e-5, rtol=1e-5)
     index = torch.tensor([7, 0, 7, 3], dtype=torch.int32, device=device)
     some = torch.empty(4, hidden, dtype=BF16, device=device)
     ops.grouped_rmsnorm(x, w, 1e-5, groups, some, index)
@@ -177,17 +184,48 @@ def test_linear_attention_whole_portions_and_single_tokens(device, heads, dim, v
     offsets = (0, qn, qn + kn)
     dev = proj.to(device)
     tol = dict(atol=2e-4 * float(want.abs().max()), rtol=1e-4)
-    for cuts in ([T], [1] * 20 + [2, 30, 3, 15], [33, 1, 1, 35]):
+    # the last two: portions longer than a segment (of 16 and of 7 tokens here) run as segments side by side
+    for cuts, segment in (([T], None), ([1] * 20 + [2, 30, 3, 15], None), ([33, 1, 1, 35], None), ([T], 16),
+                          ([9, 40, 1, 20], 7)):
         state = torch.full((3, heads, vdim, dim), 7.0, device=device)
         state[1].zero_()  # the request's slot; the others must stay as they are
         pos = 0
         for n in cuts:
             ctx = fake_ctx(device, [n], [pos], [1])
             out = torch.empty(n, heads * vdim, device=device)
-            ops.linear_attention(dev[pos:pos + n], offsets, out, state, decay, ctx, heads, dim, vdim, silu=True)
-            assert torch.allclose(out.cpu().double(), want[pos:pos + n], **tol), (cuts, pos)
+            ops.linear_attention(dev[pos:pos + n], offsets, out, state, decay, ctx, heads, dim, vdim, silu=True,
+                                 segment=segment)
+            assert torch.allclose(out.cpu().double(), want[pos:pos + n], **tol), (cuts, segment, pos)
             pos += n
         assert bool((state[0] == 7).all()) and bool((state[2] == 7).all())
+
+
+def test_linear_attention_segments_of_several_requests(device):
+    """Three requests of unequal length in one step, two of them longer than a segment, one a single token, each from
+    a state of its own: every request's outputs and final state equal those of the request run alone, unsegmented."""
+    ops = _ops()
+    torch.manual_seed(3)
+    heads, dim, vdim = 2, 48, 24
+    lens, slots = [50, 1, 37], [2, 0, 3]
+    width = 2 * heads * dim + heads * vdim
+    proj = torch.randn(sum(lens), width, device=device) * 0.7
+    decay = torch.tensor([0.98, 0.8], device=device)
+    start = torch.randn(4, heads, vdim, dim, device=device)
+    offsets = (0, heads * dim, 2 * heads * dim)
+    together = start.clone()
+    out = torch.empty(sum(lens), heads * vdim, device=device)
+    ops.linear_attention(proj, offsets, out, together, decay, fake_ctx(device, lens, [5, 9, 0], slots), heads, dim, vdim,
+                         silu=True, segment=16)
+    alone = start.clone()
+    row = 0
+    for n, slot in zip(lens, slots):
+        one = torch.empty(n, heads * vdim, device=device)
+        ops.linear_attention(proj[row:row + n], offsets, one, alone, decay, fake_ctx(device, [n], [0], [slot]), heads, dim,
+                             vdim, silu=True, segment=1000)
+        assert torch.allclose(out[row:row + n], one, atol=1e-4, rtol=1e-4), slot
+        row += n
+    assert torch.allclose(together, alone, atol=1e-4, rtol=1e-4)
+    assert torch.equal(together[1], start[1])  # a slot that no request of the step holds
 
 
 def test_linear_attention_keeps_a_key_from_hundreds_of_tokens_ago(device):
