@@ -162,9 +162,10 @@ def fill_cache(engine, batch, context):
 
     cache = engine.runner.cache
     for lc in cache.layer_caches:
-        if lc is not None and lc.k is not None:
-            lc.k.normal_(0.0, 0.5)
-            lc.v.normal_(0.0, 0.5)
+        for leaf in ([] if lc is None else lc.leaves()):
+            if leaf.k is not None:
+                leaf.k.normal_(0.0, 0.5)
+                leaf.v.normal_(0.0, 0.5)
     ids = []
     for b in range(batch):
         rid = f"bench{b}"
@@ -551,9 +552,27 @@ def main() -> int:
                     help="instead of the measurement: the timeline of one decode step (or of one prefill of 2,048 "
                          "tokens) from hooks inside the kernels (a build of the kernel library of its own; prints a "
                          "table, no JSON line)")
+    ap.add_argument("--designs", nargs="?", const="small,1B-like", default=None,
+                    help="instead of the measurement: the Kugilix decoder beside the Qwen2 decoder at equal layer sizes "
+                         "(names of bench_designs.SIZES, with commas): prefill and decode through the step function, and "
+                         "the Kugilix design's own kernels alone; prints one JSON line of its own")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.designs:
+        import bench_designs
+
+        peaks, peak_source = load_peaks()
+        clocks = ClockSampler()
+        clocks.start()
+        sizes = [n for n in args.designs.split(",") if n]
+        result = bench_designs.run(build_engine, time_decode, time_prefill, peaks, steps=min(args.steps, 32),
+                                   warmup=max(args.warmup, 3), sizes=sizes, kernels_at=sizes[-1])
+        result.update(metric="two designs at equal layer sizes: prefill and decode tok/s, kernels alone", dtype="bf16",
+                      data="synthetic (seeded uniform token ids, random-init weights)", peaks=peak_source,
+                      clocks=clocks.stop())
+        print(json.dumps(result))
+        return 0
     if args.timeline:
         return timeline(args)
     if args.gpus != 1:

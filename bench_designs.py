@@ -1,0 +1,202 @@
+"""Two designs side by side at equal layer sizes: the Kugilix decoder beside the Qwen2 dense decoder, random weights.
+
+Called by ``bench.py --designs``.  For each of a few sizes that resemble a real model's layers it measures, through
+the step function, the prefill of one prompt and decode steps at two batch sizes for both designs, and times the
+kernels that only the Kugilix design has (decayed linear attention, the windowed attention with slopes, the short
+convolution, the norms in groups, the gated norm, the activation) alone, with what they reach of the measured copy
+bandwidth or, where they are bound by fp32 arithmetic, of the nominal fp32 rate.
+"""
+
+from __future__ import annotations
+
+import math
+import statistics
+
+FP32_NOMINAL_TFLOPS = 80.0  # B200, fp32 FMAs outside the tensor cores (nominal; there is no measured figure)
+
+SIZES = {
+    # name: width, heads, kv heads, head size, feed-forward, layers of the Kugilix model (a span of four runs twice)
+    "1B-like": dict(width=2048, heads=16, kv_heads=4, dim=128, ff=8192, layers=8),
+    "3B-like": dict(width=3072, heads=24, kv_heads=8, dim=128, ff=12288, layers=8),
+    "small": dict(width=1024, heads=16, kv_heads=8, dim=64, ff=4096, layers=8),
+}
+WINDOW = 1024
+VOCAB = 32000
+
+
+def kugilix_config(s: dict) -> dict:
+    att = {"type": "attention",
+           "mixer": {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"],
+                     "scale": 1.0 / math.sqrt(s["dim"]), "mask": {"size": WINDOW}, "q_temp": {"coef": 0.3, "every": 128}},
+           "mlp": {"kind": "dense", "ff": s["ff"]}}
+    lin = {"type": "lightning",
+           "mixer": {"heads": s["heads"], "dim": s["dim"], "vdim": s["dim"],
+                     "decay": [round(1.0 - 2.0 ** (-2 - 6 * h / s["heads"]), 6) for h in range(s["heads"])]},
+           "mlp": {"kind": "dense", "ff": s["ff"]}}
+    order = [att, lin, lin, att, lin, lin, att, lin]
+    layers = [order[i % len(order)] for i in range(s["layers"])]
+    return {"architecture": "Kugilix", "vocab": VOCAB, "width": s["width"], "embedding": {"scale": math.sqrt(s["width"])},
+            "norm": {"eps": 1e-6, "groups": 4}, "canon": {"taps": 4}, "layers": layers,
+            "loop": {"start": 2, "stop": 6, "times": 2}}
+
+
+def kugilix_runs(s: dict) -> int:
+    return s["layers"] + 4
+
+
+def qwen2_config(s: dict) -> dict:
+    """The closest existing design with as many layer runs, the same width and heads, and a gated feed-forward of as
+    many weights as the plain one (three matrices of 2/3 the width), every layer over the same window."""
+    inter = (2 * s["ff"] // 3 + 127) // 128 * 128
+    n = kugilix_runs(s)
+    return {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "vocab_size": VOCAB, "hidden_size": s["width"],
+            "intermediate_size": inter, "num_hidden_layers": n, "num_attention_heads": s["heads"],
+            "num_key_value_heads": s["kv_heads"], "head_dim": s["dim"], "max_position_embeddings": 8192,
+            "rms_norm_eps": 1e-6, "rope_theta": 1e6, "hidden_act": "silu", "tie_word_embeddings": False,
+            "use_sliding_window": True, "sliding_window": WINDOW, "max_window_layers": 0}
+
+
+def _timed(fn, flush, warmup=3, iters=5):
+    import torch
+
+    for _ in range(warmup):
+        fn()
+    times = []
+    for _ in range(iters):
+        flush.add_(1.0)  # write a buffer larger than L2 between timed launches
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    return statistics.median(times) * 1e-3
+
+
+def kernel_numbers(s: dict, peaks: dict) -> dict:
+    """The Kugilix design's own kernels alone at the layer sizes ``s``: seconds, and the fraction of the roofline each
+    is measured against (``hbm``: bytes that must move over the measured copy bandwidth; ``fp32``: FMAs over the
+    nominal fp32 rate)."""
+    import torch
+    from types import SimpleNamespace
+
+    from ferrisinfer_b200.kernels import ops
+    from ferrisinfer_b200.parts.position import DistanceSlopes
+
+    dev = torch.device("cuda")
+    bf = torch.bfloat16
+    flush = torch.zeros(96 << 20, dtype=torch.float32, device=dev)  # 384 MB
+    W, H, G, d, ff = s["width"], s["heads"], s["kv_heads"], s["dim"], s["ff"]
+    hbm = peaks["hbm_gbs"] * 1e9
+    out = {}
+
+    def ctx_of(q_lens, start):
+        S = len(q_lens)
+        q_start = [0]
+        for n in q_lens:
+            q_start.append(q_start[-1] + n)
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+        return SimpleNamespace(num_tokens=q_start[-1], num_seqs=S, max_q_len=max(q_lens), workspace=None,
+                               token_seq=i32([i for i in range(S) for _ in range(q_lens[i])]),
+                               positions=i32([start + j for i in range(S) for j in range(q_lens[i])]),
+                               seq_q_start=i32(q_start), seq_start_pos=i32([start] * S), seq_state_slot=i32(list(range(S))))
+
+    def record(name, seconds, bytes_=None, flops=None):
+        e = {"us": round(seconds * 1e6, 1)}
+        if bytes_ is not None:
+            e["GBps"] = round(bytes_ / seconds / 1e9, 1)
+            e["frac_hbm"] = round(bytes_ / seconds / hbm, 3)
+        if flops is not None:
+            e["TFLOPs_fp32"] = round(flops / seconds / 1e12, 2)
+            e["frac_fp32_nominal"] = round(flops / seconds / (FP32_NOMINAL_TFLOPS * 1e12), 3)
+        out[name] = e
+
+    # ---- decayed linear attention
+    for name, q_lens in (("linear_attention_decode_b64", [1] * 64), ("linear_attention_prefill_2048", [2048])):
+        T, S = sum(q_lens), len(q_lens)
+        proj = torch.randn(T, 4 * H * d, device=dev).to(bf)
+        state = torch.zeros(S + 1, H, d, d, device=dev)
+        o = torch.empty(T, H * d, device=dev)
+        decay = torch.full((H,), 0.97, device=dev)
+        ctx = ctx_of(q_lens, 0)
+        t = _timed(lambda: ops.linear_attention(proj, (0, H * d, 2 * H * d), o, state, decay, ctx, H, d, d, silu=True), flush)
+        moved = 2 * S * H * d * d * 4 + T * 3 * H * d * 2 + T * H * d * 4
+        record(name, t, bytes_=moved, flops=4.0 * T * H * d * d)
+    # ---- windowed attention with unit-norm keys and slopes
+    slopes = DistanceSlopes(8.0).score_slopes(H, dev)
+    for name, batch, q_len, ctx_len in (("window_attention_decode_b64", 64, 1, 2048), ("window_attention_prefill_2048", 1, 2048, 0)):
+        T = batch * q_len
+        pages_each = (ctx_len + q_len + 15) // 16
+        k = torch.randn(batch * pages_each + 1, G, 16, d, device=dev).to(bf)
+        v = torch.randn_like(k)
+        tables = torch.arange(batch * pages_each, dtype=torch.int32, device=dev).view(batch, pages_each)
+        qkv = torch.randn(T, (H + 2 * G) * d, device=dev).to(bf)
+        o = torch.empty(T, H * d, dtype=bf, device=dev)
+        ctx = ctx_of([q_len] * batch, ctx_len)
+        t = _timed(lambda: ops.paged_attention_simt(qkv, o, k, v, tables, ctx.token_seq, ctx.positions, H, G, d, WINDOW,
+                                                    1.0 / math.sqrt(d), score_slopes=slopes, v_head_dim=d), flush)
+        keys = sum(min(WINDOW, ctx_len + j + 1) for j in range(q_len)) * batch
+        if q_len == 1:
+            record(name, t, bytes_=batch * G * min(WINDOW, ctx_len + 1) * 2 * d * 2 + T * H * d * 4, flops=4.0 * keys * H * d)
+        else:
+            record(name, t, flops=4.0 * keys * H * d)
+        slots = (tables[ctx.token_seq.long(), (ctx.positions // 16).long()] * 16 + ctx.positions % 16).int()
+        t = _timed(lambda: ops.qk_prepare_cache_write(qkv, ctx.positions, slots, k, v, H, G, d, d, 1e-6, (0.3, 128)), flush)
+        record(name.replace("window_attention", "qk_prepare"), t, bytes_=T * (2 * H * d + 4 * G * d) * 2)
+    # ---- row-wise kernels of a long step and of a decode step
+    for tag, T in (("2048", 2048), ("b64", 64)):
+        h = torch.randn(T, W, device=dev)
+        w1, w2 = torch.ones(W, device=dev), torch.ones(W, device=dev)
+        a, b = torch.empty(T, W, dtype=bf, device=dev), torch.empty(T, W, dtype=bf, device=dev)
+        t = _timed(lambda: ops.grouped_rmsnorm_pair(h, w1, w2, 1e-6, 4, a, b), flush)
+        record(f"norm_pair_{tag}", t, bytes_=T * W * (4 + 2 + 2))
+        cw = torch.randn(W, 4, device=dev) * 0.1
+        cs = torch.zeros(T + 1, 3, W, device=dev)
+        ctx = ctx_of([T], 0) if T > 64 else ctx_of([1] * T, 5)
+        t = _timed(lambda: ops.short_conv(a, b, cw, cs, ctx), flush)
+        record(f"short_conv_{tag}", t, bytes_=T * W * 4 + (ctx.num_seqs * 3 * W * 8 if T <= 64 else 0))
+        z = torch.randn(T, ff, device=dev).to(bf)
+        pq = torch.tensor([0.3, -0.2], device=dev)
+        t = _timed(lambda: ops.activation(z, z, "xielu", pq), flush)
+        record(f"xielu_{tag}", t, bytes_=T * ff * 4)
+        o = torch.randn(T, H * d, device=dev)
+        g = torch.randn(T, H * d, device=dev).to(bf)
+        y = torch.empty(T, H * d, dtype=bf, device=dev)
+        nw = torch.ones(H * d, device=dev)
+        t = _timed(lambda: ops.gated_rmsnorm(o, g, nw, 1e-6, y), flush)
+        record(f"gated_norm_{tag}", t, bytes_=T * H * d * (4 + 2 + 2))
+    return out
+
+
+def run(build_engine, time_decode, time_prefill, peaks, steps=32, warmup=4, sizes=("small", "1B-like"), context=2048,
+        prompt=2048, batches=(8, 64), kernels_at="1B-like") -> dict:
+    """``build_engine(cfg, batch, context, extra_tokens)``, ``time_decode`` and ``time_prefill`` are bench.py's."""
+    import torch
+
+    result = {"context": context, "prompt_tokens": prompt, "window": WINDOW, "sizes": {}}
+    for name in sizes:
+        s = SIZES[name]
+        entry = {"layer_sizes": s, "layer_runs": kugilix_runs(s)}
+        for design, cfg in (("kugilix", kugilix_config(s)), ("qwen2", qwen2_config(s))):
+            numbers = {}
+            engine = build_engine(cfg, 1, context, extra_tokens=prompt)
+            ms = time_prefill(engine, prompt)
+            numbers["prefill_tok_s"] = round(prompt / ms * 1e3, 1)
+            numbers["prefill_ms"] = round(ms, 3)
+            del engine
+            torch.cuda.empty_cache()
+            for b in batches:
+                engine = build_engine(cfg, b, context)
+                times, launches = time_decode(engine, b, context, steps, warmup, regions=3)
+                ms = statistics.median(times)
+                numbers[f"decode_b{b}_tok_s"] = round(b / ms * 1e3, 1)
+                numbers[f"decode_b{b}_ms"] = round(ms, 4)
+                numbers[f"decode_b{b}_launches_per_step"] = launches // steps
+                del engine
+                torch.cuda.empty_cache()
+            entry[design] = numbers
+        result["sizes"][name] = entry
+    if kernels_at:
+        result["kernels"] = {"at": kernels_at, **kernel_numbers(SIZES[kernels_at], peaks)}
+    return result

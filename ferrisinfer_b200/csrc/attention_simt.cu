@@ -110,6 +110,197 @@ __global__ void __launch_bounds__(ATT_THREADS)
     }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// The same attention for head sizes that are multiples of eight: EIGHT lanes share a key, so a warp has four keys
+// in flight (a block sixteen, two each where registers allow), and every lane reads its eighth of a key or value
+// row with the widest loads its size allows (16 bytes at head sizes that are multiples of 64 in bf16).  The dot
+// product is summed over the eight lanes with three shuffles; each group of eight keeps a running maximum, sum
+// and weighted value sum of its own over its keys lo + g, lo + g + 16, ...; the sixteen groups are merged at the end
+// as the four warps are in the kernel above.  Scores, weights and sums are fp32.
+// ---------------------------------------------------------------------------------------------
+constexpr int AL_THREADS = 128;
+constexpr int AL_GROUPS = AL_THREADS / 8;
+
+template <int MAXC>
+__device__ __forceinline__ void load_chunk(const float* p, int n, float (&o)[MAXC]) {
+    if ((n & 3) == 0) {
+#pragma unroll
+        for (int i = 0; i < MAXC; i += 4)
+            if (i < n) {
+                const float4 u = *reinterpret_cast<const float4*>(p + i);
+                o[i] = u.x, o[i + 1] = u.y, o[i + 2] = u.z, o[i + 3] = u.w;
+            }
+    } else {
+#pragma unroll
+        for (int i = 0; i < MAXC; ++i)
+            if (i < n) o[i] = p[i];
+    }
+}
+
+__device__ __forceinline__ float bf16_lo(uint32_t u) { return __uint_as_float(u << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t u) { return __uint_as_float(u & 0xffff0000u); }
+
+template <int MAXC>
+__device__ __forceinline__ void load_chunk(const bf16* p, int n, float (&o)[MAXC]) {
+    if ((n & 7) == 0) {
+#pragma unroll
+        for (int i = 0; i < MAXC; i += 8)
+            if (i < n) {
+                const uint4 u = *reinterpret_cast<const uint4*>(p + i);
+                o[i] = bf16_lo(u.x), o[i + 1] = bf16_hi(u.x), o[i + 2] = bf16_lo(u.y), o[i + 3] = bf16_hi(u.y);
+                o[i + 4] = bf16_lo(u.z), o[i + 5] = bf16_hi(u.z), o[i + 6] = bf16_lo(u.w), o[i + 7] = bf16_hi(u.w);
+            }
+    } else if ((n & 3) == 0) {
+#pragma unroll
+        for (int i = 0; i < MAXC; i += 4)
+            if (i < n) {
+                const uint2 u = *reinterpret_cast<const uint2*>(p + i);
+                o[i] = bf16_lo(u.x), o[i + 1] = bf16_hi(u.x), o[i + 2] = bf16_lo(u.y), o[i + 3] = bf16_hi(u.y);
+            }
+    } else if ((n & 1) == 0) {
+#pragma unroll
+        for (int i = 0; i < MAXC; i += 2)
+            if (i < n) {
+                const uint32_t u = *reinterpret_cast<const uint32_t*>(p + i);
+                o[i] = bf16_lo(u), o[i + 1] = bf16_hi(u);
+            }
+    } else {
+#pragma unroll
+        for (int i = 0; i < MAXC; ++i)
+            if (i < n) o[i] = __bfloat162float(p[i]);
+    }
+}
+
+// MAXC: most elements of a head that one lane holds (d, dv <= 8 * MAXC).  U: keys of a group in flight together.
+template <typename T, int MAXC, int U>
+__global__ void __launch_bounds__(AL_THREADS)
+    paged_attention_lanes_kernel(const T* q, int ldq, T* __restrict__ out, int ldo, const T* k_cache, const T* v_cache,
+                                 const int* __restrict__ block_tables, int max_blocks,
+                                 const int* __restrict__ token_seq, const int* __restrict__ positions, int nh, int nkv,
+                                 int d, int dv, int page_size, int window, float scale,
+                                 const float* __restrict__ slopes) {
+    extern __shared__ float smem[];  // per group: m, z, acc[dv]
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t = blockIdx.x, hq = blockIdx.y;
+    const int sub = threadIdx.x & 7, grp = threadIdx.x >> 3;
+    const int hk = hq / (nh / nkv);
+    const int seq = token_seq[t];
+    const int P = positions[t];
+    const int lo = (window > 0 && P - window + 1 > 0) ? P - window + 1 : 0;
+    const int* table = block_tables + (size_t)seq * max_blocks;
+    const float slope = slopes ? slopes[hq] : 0.0f;
+    const int ch = d >> 3, cv = dv >> 3;
+    const int pshift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
+
+    float qv[MAXC], acc[MAXC];
+#pragma unroll
+    for (int i = 0; i < MAXC; ++i) qv[i] = 0.0f, acc[i] = 0.0f;
+    load_chunk<MAXC>(q + (size_t)t * ldq + (size_t)hq * d + sub * ch, ch, qv);
+    float m = -INFINITY, z = 0.0f;
+    const int rounds = (P - lo + AL_GROUPS * U) / (AL_GROUPS * U);  // every lane of a warp makes as many: the shuffles need all
+    for (int it = 0; it < rounds; ++it) {
+        float kk[U][MAXC], vv[U][MAXC];
+        bool ok[U];
+        int jj[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int j = lo + (it * U + u) * AL_GROUPS + grp;
+            jj[u] = j;
+            int page = -1;
+            if (j <= P) page = table[pshift >= 0 ? (j >> pshift) : (j / page_size)];
+            ok[u] = page >= 0;  // beyond the last key, or a hole in the table (never for keys inside the window)
+            const int in_page = pshift >= 0 ? (j & (page_size - 1)) : (j % page_size);
+            const size_t row = ((size_t)(ok[u] ? page : 0) * nkv + hk) * page_size + (ok[u] ? in_page : 0);
+#pragma unroll
+            for (int i = 0; i < MAXC; ++i) kk[u][i] = 0.0f, vv[u][i] = 0.0f;
+            if (ok[u]) {
+                load_chunk<MAXC>(k_cache + row * d + sub * ch, ch, kk[u]);
+                load_chunk<MAXC>(v_cache + row * dv + sub * cv, cv, vv[u]);
+            }
+        }
+        float dot[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            float a = 0.0f;
+#pragma unroll
+            for (int i = 0; i < MAXC; ++i) a = fmaf(qv[i], kk[u][i], a);
+            dot[u] = a;
+        }
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1)
+#pragma unroll
+            for (int u = 0; u < U; ++u) dot[u] += __shfl_xor_sync(0xffffffffu, dot[u], o);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (!ok[u]) continue;
+            const float s = slopes ? fmaf(slope, (float)(jj[u] - P), dot[u] * scale) : dot[u] * scale;
+            float wgt;
+            if (s > m) {
+                const float rescale = expf(m - s);  // exp(-inf) = 0 on the first key
+#pragma unroll
+                for (int i = 0; i < MAXC; ++i) acc[i] *= rescale;
+                z = z * rescale + 1.0f;
+                m = s;
+                wgt = 1.0f;
+            } else {
+                wgt = expf(s - m);
+                z += wgt;
+            }
+#pragma unroll
+            for (int i = 0; i < MAXC; ++i) acc[i] = fmaf(wgt, vv[u][i], acc[i]);
+        }
+    }
+    float* mine = smem + grp * (dv + 2);
+    if (sub == 0) {
+        mine[0] = m;
+        mine[1] = z;
+    }
+#pragma unroll
+    for (int i = 0; i < MAXC; ++i)
+        if (i < cv) mine[2 + sub * cv + i] = acc[i];
+    __syncthreads();
+    float mm = -INFINITY;
+    for (int g = 0; g < AL_GROUPS; ++g) mm = fmaxf(mm, smem[g * (dv + 2)]);
+    float zz = 0.0f;
+    float f[AL_GROUPS];
+#pragma unroll
+    for (int g = 0; g < AL_GROUPS; ++g) {
+        const float mg = smem[g * (dv + 2)];
+        f[g] = mg == -INFINITY ? 0.0f : expf(mg - mm);
+        zz += smem[g * (dv + 2) + 1] * f[g];
+    }
+    const float inv = 1.0f / zz;
+    T* orow = out + (size_t)t * ldo + (size_t)hq * dv;
+    for (int i = threadIdx.x; i < dv; i += AL_THREADS) {
+        float o = 0.0f;
+#pragma unroll
+        for (int g = 0; g < AL_GROUPS; ++g) o += smem[g * (dv + 2) + 2 + i] * f[g];
+        orow[i] = from_float<T>(o * inv);
+    }
+}
+
+template <typename T>
+void launch_lanes(const void* q, int ldq, void* out, int ldo, const void* k_cache, const void* v_cache,
+                  const int* block_tables, int max_blocks, const int* token_seq, const int* positions, int tokens, int nh,
+                  int nkv, int d, int dv, int page_size, int window, float scale, const float* slopes, cudaStream_t s) {
+    const dim3 grid(tokens, nh), block(AL_THREADS);
+    const size_t smem = (size_t)AL_GROUPS * (dv + 2) * sizeof(float);
+    const int most = d > dv ? d : dv;
+#define FERRIS_AL_LAUNCH(MAXC, U)                                                                                      \
+    ferris_launch(paged_attention_lanes_kernel<T, MAXC, U>, grid, block, smem, s, (const T*)q, ldq, (T*)out, ldo,      \
+                  (const T*)k_cache, (const T*)v_cache, block_tables, max_blocks, token_seq, positions, nh, nkv, d, dv, \
+                  page_size, window, scale, slopes)
+    if (most <= 64)
+        FERRIS_AL_LAUNCH(8, 2);
+    else if (most <= 128)
+        FERRIS_AL_LAUNCH(16, 2);
+    else
+        FERRIS_AL_LAUNCH(32, 1);
+#undef FERRIS_AL_LAUNCH
+}
+
 }  // namespace
 
 FERRIS_API int ferris_paged_attention_simt(const void* q, int ldq, void* out, int ldo, const void* k_cache,
@@ -126,6 +317,17 @@ FERRIS_API int ferris_paged_attention_simt(const void* q, int ldq, void* out, in
     dim3 grid(tokens, nh);
     const size_t smem = (size_t)ATT_WARPS * (dv + 2) * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
+    if (dtype != FERRIS_F32 && dtype != FERRIS_BF16) FERRIS_REFUSE("attention: unknown dtype %d", dtype);
+    // head sizes that eight lanes can share evenly, rows that start on 16 bytes: the kernel with eight lanes to a key
+    const size_t elt = dtype == FERRIS_F32 ? 4 : 2;
+    const bool aligned = (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) == 0 && ((size_t)ldq * elt) % 16 == 0;
+    if (d % 8 == 0 && dv % 8 == 0 && aligned && (size_t)AL_GROUPS * (dv + 2) * sizeof(float) <= 48 * 1024) {
+        if (dtype == FERRIS_F32)
+            launch_lanes<float>(q, ldq, out, ldo, k_cache, v_cache, block_tables, max_blocks, token_seq, positions, tokens, nh, nkv, d, dv, page_size, window, scale, slopes, s);
+        else
+            launch_lanes<bf16>(q, ldq, out, ldo, k_cache, v_cache, block_tables, max_blocks, token_seq, positions, tokens, nh, nkv, d, dv, page_size, window, scale, slopes, s);
+        FERRIS_LAUNCH_CHECK();
+    }
     if (dtype == FERRIS_F32)
         ferris_launch(paged_attention_simt_kernel<float>, grid, dim3(ATT_THREADS), smem, s, (const float*)q, ldq, (float*)out, ldo, (const float*)k_cache, (const float*)v_cache, block_tables,
             max_blocks, token_seq, positions, nh, nkv, d, dv, page_size, window, scale, slopes);
