@@ -301,6 +301,240 @@ void launch_lanes(const void* q, int ldq, void* out, int ldo, const void* k_cach
 #undef FERRIS_AL_LAUNCH
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Portions of prompts: a block takes TL_ROWS = 64 query rows that share their keys and values, namely the g query heads
+// of one kv head for 64 / g consecutive tokens of the step, and walks the keys those tokens see in tiles of 32, which
+// it brings into shared memory once for all 64 rows (fp32, a row's 16-byte pieces spread over the banks).  Eight
+// lanes share two rows: each forms 2 x 4 scores of a tile from shared memory, the eight exchange the rows' maxima
+// and sums by shuffles, write the weights to shared memory and add 2 x (dv / 8) columns of weighted values each.
+// Everything is fp32 FMAs: scores, weights and the sums over values.  Tokens of several requests in one tile are taken
+// request by request (the other rows masked), so any division of a step is served; a step of single tokens is the
+// kernel above's.
+// ---------------------------------------------------------------------------------------------
+constexpr int TL_ROWS = 64, TL_KEYS = 32, TL_THREADS = 256;
+
+__device__ __forceinline__ void stage_row(const float* src, float* dst, int n, int part, int parts, float mul) {
+    for (int v = part; v * 4 < n; v += parts) {
+        float4 u = *reinterpret_cast<const float4*>(src + v * 4);
+        u.x *= mul, u.y *= mul, u.z *= mul, u.w *= mul;
+        *reinterpret_cast<float4*>(dst + v * 4) = u;
+    }
+}
+__device__ __forceinline__ void stage_row(const bf16* src, float* dst, int n, int part, int parts, float mul) {
+    for (int v = part; v * 8 < n; v += parts) {
+        const uint4 u = *reinterpret_cast<const uint4*>(src + v * 8);
+        *reinterpret_cast<float4*>(dst + v * 8) = make_float4(bf16_lo(u.x) * mul, bf16_hi(u.x) * mul, bf16_lo(u.y) * mul, bf16_hi(u.y) * mul);
+        *reinterpret_cast<float4*>(dst + v * 8 + 4) = make_float4(bf16_lo(u.z) * mul, bf16_hi(u.z) * mul, bf16_lo(u.w) * mul, bf16_hi(u.w) * mul);
+    }
+}
+__device__ __forceinline__ void zero_row(float* dst, int n, int part, int parts) {
+    for (int v = part; v * 4 < n; v += parts) *reinterpret_cast<float4*>(dst + v * 4) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+}
+
+template <typename T, int NC>  // NC: 4-column pieces of the value head that a lane adds up: dv <= 32 * NC
+__global__ void __launch_bounds__(TL_THREADS)
+    paged_attention_tiled_kernel(const T* q, int ldq, T* __restrict__ out, int ldo, const T* k_cache, const T* v_cache,
+                                 const int* __restrict__ block_tables, int max_blocks,
+                                 const int* __restrict__ token_seq, const int* __restrict__ positions, int tokens, int nh,
+                                 int nkv, int d, int dv, int page_size, int window, float scale,
+                                 const float* __restrict__ slopes) {
+    extern __shared__ __align__(16) float tl_smem[];
+    const int dp = d + 4, dvp = dv + 4;
+    float* Qs = tl_smem;                      // [64][d + 4], scaled
+    float* Ks = Qs + TL_ROWS * dp;            // [32][d + 4]
+    float* Vs = Ks + TL_KEYS * dp;            // [32][dv + 4]
+    float* Ps = Vs + TL_KEYS * dvp;           // [64][32 + 1]
+    pdl_wait();
+    pdl_launch_dependents();
+    const int tid = threadIdx.x;
+    const int g = nh / nkv, qt = TL_ROWS / g;
+    const int hk = blockIdx.y;
+    const int t_first = blockIdx.x * qt;
+    const int t_end = min(t_first + qt, tokens);
+    const int pshift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
+
+    // the queries, scaled once
+    {
+        const int row = tid >> 2, part = tid & 3;
+        const int t = t_first + row / g;
+        float* dst = Qs + row * dp;
+        if (t < t_end)
+            stage_row(q + (size_t)t * ldq + (size_t)(hk * g + row % g) * d, dst, d, part, 4, scale);
+        else
+            zero_row(dst, d, part, 4);
+    }
+    const int ry = tid >> 3, kx = tid & 7;
+    const int r0 = 2 * ry;  // this lane's rows: r0 and r0 + 1
+    int rt[2], rpos[2], rseq[2];
+    float rslope[2];
+#pragma unroll
+    for (int a = 0; a < 2; ++a) {
+        rt[a] = t_first + (r0 + a) / g;
+        const bool ok = rt[a] < t_end;
+        rpos[a] = ok ? positions[rt[a]] : -1;
+        rseq[a] = ok ? token_seq[rt[a]] : -1;
+        rslope[a] = slopes ? slopes[hk * g + (r0 + a) % g] : 0.0f;
+    }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+    float acc[2][NC][4];
+#pragma unroll
+    for (int a = 0; a < 2; ++a)
+#pragma unroll
+        for (int c = 0; c < NC; ++c)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[a][c][e] = 0.0f;
+
+    const int seq_first = token_seq[t_first], seq_last = token_seq[t_end - 1];
+    int ta = t_first;  // first token of the current request within the tile
+    for (int sq = seq_first; sq <= seq_last; ++sq) {
+        int tb = ta;  // its last token within the tile
+        while (tb + 1 < t_end && token_seq[tb + 1] == sq) ++tb;
+        const int pa = positions[ta], pb = positions[tb];
+        const int kmin = (window > 0 && pa - window + 1 > 0) ? pa - window + 1 : 0;
+        const int* table = block_tables + (size_t)sq * max_blocks;
+        for (int j0 = kmin & ~(TL_KEYS - 1); j0 <= pb; j0 += TL_KEYS) {
+            __syncthreads();  // the tile before has been used (and, the first time, the queries are in place)
+            {
+                const int key = tid >> 3, part = tid & 7;
+                const int j = j0 + key;
+                int page = -1;
+                if (j >= kmin && j <= pb) page = table[pshift >= 0 ? (j >> pshift) : (j / page_size)];
+                if (page >= 0) {
+                    const int in_page = pshift >= 0 ? (j & (page_size - 1)) : (j % page_size);
+                    const size_t row = ((size_t)page * nkv + hk) * page_size + in_page;
+                    stage_row(k_cache + row * d, Ks + key * dp, d, part, 8, 1.0f);
+                    stage_row(v_cache + row * dv, Vs + key * dvp, dv, part, 8, 1.0f);
+                } else {
+                    zero_row(Ks + key * dp, d, part, 8);
+                    zero_row(Vs + key * dvp, dv, part, 8);
+                }
+            }
+            __syncthreads();
+            // 2 x 4 scores: rows r0, r0 + 1 against keys kx, kx + 8, kx + 16, kx + 24
+            float sc[2][4];
+#pragma unroll
+            for (int a = 0; a < 2; ++a)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) sc[a][c] = 0.0f;
+            const float* q0 = Qs + r0 * dp;
+            const float* kb = Ks + kx * dp;
+            for (int x = 0; x < d; x += 4) {
+                const float4 qa = *reinterpret_cast<const float4*>(q0 + x);
+                const float4 qb = *reinterpret_cast<const float4*>(q0 + dp + x);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const float4 kv = *reinterpret_cast<const float4*>(kb + (size_t)(8 * c) * dp + x);
+                    sc[0][c] = fmaf(qa.x, kv.x, fmaf(qa.y, kv.y, fmaf(qa.z, kv.z, fmaf(qa.w, kv.w, sc[0][c]))));
+                    sc[1][c] = fmaf(qb.x, kv.x, fmaf(qb.y, kv.y, fmaf(qb.z, kv.z, fmaf(qb.w, kv.w, sc[1][c]))));
+                }
+            }
+            // the rows' maxima and sums over the tile, among the eight lanes that share the rows
+            float alpha[2];
+#pragma unroll
+            for (int a = 0; a < 2; ++a) {
+                const int lo = (window > 0 && rpos[a] - window + 1 > 0) ? rpos[a] - window + 1 : 0;
+                float best = -INFINITY;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int j = j0 + kx + 8 * c;
+                    const bool seen = rseq[a] == sq && j >= lo && j <= rpos[a];
+                    sc[a][c] = seen ? fmaf(rslope[a], (float)(j - rpos[a]), sc[a][c]) : -INFINITY;
+                    best = fmaxf(best, sc[a][c]);
+                }
+#pragma unroll
+                for (int o = 4; o > 0; o >>= 1) best = fmaxf(best, __shfl_xor_sync(0xffffffffu, best, o));
+                const float m_new = fmaxf(m[a], best);
+                alpha[a] = (m_new == -INFINITY || m[a] == m_new) ? 1.0f : expf(m[a] - m_new);  // exp(-inf) = 0 at a row's first keys
+                float sum = 0.0f;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const float pw = sc[a][c] == -INFINITY ? 0.0f : expf(sc[a][c] - m_new);
+                    Ps[(r0 + a) * (TL_KEYS + 1) + kx + 8 * c] = pw;
+                    sum += pw;
+                }
+#pragma unroll
+                for (int o = 4; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+                l[a] = l[a] * alpha[a] + sum;
+                m[a] = m_new;
+            }
+            __syncwarp();  // a row's weights are written and read by the same eight lanes
+#pragma unroll
+            for (int a = 0; a < 2; ++a)
+#pragma unroll
+                for (int c = 0; c < NC; ++c)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) acc[a][c][e] *= alpha[a];
+            const float* p0 = Ps + r0 * (TL_KEYS + 1);
+            for (int kj = 0; kj < TL_KEYS; ++kj) {
+                const float pa0 = p0[kj], pa1 = p0[TL_KEYS + 1 + kj];
+                const float* vrow = Vs + kj * dvp + kx * 4;
+#pragma unroll
+                for (int c = 0; c < NC; ++c) {
+                    if (kx * 4 + 32 * c < dv) {
+                        const float4 vv = *reinterpret_cast<const float4*>(vrow + 32 * c);
+                        acc[0][c][0] = fmaf(pa0, vv.x, acc[0][c][0]), acc[0][c][1] = fmaf(pa0, vv.y, acc[0][c][1]);
+                        acc[0][c][2] = fmaf(pa0, vv.z, acc[0][c][2]), acc[0][c][3] = fmaf(pa0, vv.w, acc[0][c][3]);
+                        acc[1][c][0] = fmaf(pa1, vv.x, acc[1][c][0]), acc[1][c][1] = fmaf(pa1, vv.y, acc[1][c][1]);
+                        acc[1][c][2] = fmaf(pa1, vv.z, acc[1][c][2]), acc[1][c][3] = fmaf(pa1, vv.w, acc[1][c][3]);
+                    }
+                }
+            }
+        }
+        ta = tb + 1;
+    }
+#pragma unroll
+    for (int a = 0; a < 2; ++a) {
+        if (rt[a] >= t_end) continue;
+        const float inv = 1.0f / l[a];
+        T* orow = out + (size_t)rt[a] * ldo + (size_t)(hk * g + (r0 + a) % g) * dv;
+#pragma unroll
+        for (int c = 0; c < NC; ++c) {
+            const int col = kx * 4 + 32 * c;
+            if (col < dv) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) orow[col + e] = from_float<T>(acc[a][c][e] * inv);
+            }
+        }
+    }
+}
+
+size_t tiled_smem_bytes(int d, int dv) {
+    return ((size_t)(TL_ROWS + TL_KEYS) * (d + 4) + (size_t)TL_KEYS * (dv + 4) + (size_t)TL_ROWS * (TL_KEYS + 1)) * sizeof(float);
+}
+
+bool tiled_takes(int dtype, int nh, int nkv, int d, int dv) {
+    const int g = nkv > 0 ? nh / nkv : 0;
+    const int unit = dtype == FERRIS_F32 ? 4 : 8;  // elements of a 16-byte piece
+    return g >= 1 && g <= TL_ROWS && (g & (g - 1)) == 0 && nh % nkv == 0 && d % unit == 0 && dv % unit == 0 && d <= 256 &&
+           dv <= 256 && tiled_smem_bytes(d, dv) <= 200 * 1024;
+}
+
+template <typename T>
+int launch_tiled(const void* q, int ldq, void* out, int ldo, const void* k_cache, const void* v_cache,
+                 const int* block_tables, int max_blocks, const int* token_seq, const int* positions, int tokens, int nh,
+                 int nkv, int d, int dv, int page_size, int window, float scale, const float* slopes, cudaStream_t s) {
+    const int qt = TL_ROWS / (nh / nkv);
+    const dim3 grid((tokens + qt - 1) / qt, nkv), block(TL_THREADS);
+    const size_t smem = tiled_smem_bytes(d, dv);
+#define FERRIS_TL_LAUNCH(NC)                                                                                        \
+    do {                                                                                                            \
+        int e_ = ferris_allow_dynamic_smem((const void*)paged_attention_tiled_kernel<T, NC>, smem);                 \
+        if (e_ != FERRIS_OK) return e_;                                                                             \
+        ferris_launch(paged_attention_tiled_kernel<T, NC>, grid, block, smem, s, (const T*)q, ldq, (T*)out, ldo,   \
+                      (const T*)k_cache, (const T*)v_cache, block_tables, max_blocks, token_seq, positions, tokens, \
+                      nh, nkv, d, dv, page_size, window, scale, slopes);                                           \
+    } while (0)
+    if (dv <= 64)
+        FERRIS_TL_LAUNCH(2);
+    else if (dv <= 128)
+        FERRIS_TL_LAUNCH(4);
+    else
+        FERRIS_TL_LAUNCH(8);
+#undef FERRIS_TL_LAUNCH
+    FERRIS_LAUNCH_CHECK();
+}
+
 }  // namespace
 
 FERRIS_API int ferris_paged_attention_simt(const void* q, int ldq, void* out, int ldo, const void* k_cache,
@@ -337,4 +571,30 @@ FERRIS_API int ferris_paged_attention_simt(const void* q, int ldq, void* out, in
     else
         FERRIS_REFUSE("attention: unknown dtype %d", dtype);
     FERRIS_LAUNCH_CHECK();
+}
+
+// Whether ferris_paged_attention_tiled takes a geometry (head sizes in 16-byte pieces, a group of query heads that is
+// a power of two and at most 64).
+FERRIS_API int ferris_paged_attention_tiled_takes(int dtype, int nh, int nkv, int d, int dv) {
+    return tiled_takes(dtype, nh, nkv, d, dv) ? 1 : 0;
+}
+
+// The same attention as ferris_paged_attention_simt (same arguments), for steps that bring portions of prompts.
+FERRIS_API int ferris_paged_attention_tiled(const void* q, int ldq, void* out, int ldo, const void* k_cache,
+                                            const void* v_cache, int dtype, const int* block_tables, int max_blocks,
+                                            const int* token_seq, const int* positions, int tokens, int nh, int nkv,
+                                            int d, int dv, int page_size, int window, float scale, const float* slopes,
+                                            void* stream) {
+    if (tokens <= 0) return FERRIS_OK;
+    if (dtype != FERRIS_F32 && dtype != FERRIS_BF16) FERRIS_REFUSE("attention: unknown dtype %d", dtype);
+    if (page_size <= 0 || max_blocks <= 0) FERRIS_REFUSE("attention: page_size=%d max_blocks=%d", page_size, max_blocks);
+    if (!tiled_takes(dtype, nh, nkv, d, dv)) FERRIS_REFUSE("tiled attention: %d heads over %d kv heads of %d / %d are not taken", nh, nkv, d, dv);
+    const size_t elt = dtype == FERRIS_F32 ? 4 : 2;
+    if ((((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) != 0 || ((size_t)ldq * elt) % 16 != 0)
+        FERRIS_REFUSE("tiled attention: rows must start on 16 bytes");
+    if (nkv > 65535) FERRIS_REFUSE("attention: %d kv heads are more than one launch takes", nkv);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == FERRIS_F32)
+        return launch_tiled<float>(q, ldq, out, ldo, k_cache, v_cache, block_tables, max_blocks, token_seq, positions, tokens, nh, nkv, d, dv, page_size, window, scale, slopes, s);
+    return launch_tiled<bf16>(q, ldq, out, ldo, k_cache, v_cache, block_tables, max_blocks, token_seq, positions, tokens, nh, nkv, d, dv, page_size, window, scale, slopes, s);
 }

@@ -6,9 +6,10 @@
 //
 // The columns of S do not depend on one another, so a warp owns eight of them for one (request, head) and walks
 // the request's tokens of the step in order: a lane holds rows lane, lane + 32, ... of its eight columns in
-// registers, updates them with fp32 FMAs, and the eight dot products with q are summed over the warp.  No barrier,
-// no shared memory; a step of single tokens and a portion of a prompt are the same loop, and a long portion is cut
-// into segments that run side by side (see the kernel).  The state lies
+// registers, updates them with fp32 FMAs, and the eight dot products with q are summed over the warp.  The four
+// warps of a block share a head: they bring q, k and their 32 columns of v of eight tokens at a time into shared
+// memory, activation applied once, and then each walks those tokens alone.  A step of single tokens and a portion
+// of a prompt are the same loop, and a long portion is cut into segments that run side by side (see the kernel).  The state lies
 // transposed in memory, [slot, head, vdim, dim], so that a warp reads and writes whole rows of it.
 // q, k, v may be passed through SiLU on the way in (`silu`), in fp32 whatever the storage type.
 #include <math.h>
@@ -19,6 +20,8 @@ namespace {
 
 constexpr int LA_COLS = 8;
 constexpr int LA_WARPS = 4;
+constexpr int LA_STAGE = 8;      // tokens whose q, k, v stand in shared memory at a time
+constexpr int LA_MAX_DIM = 256;  // largest head size
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
 
@@ -60,24 +63,28 @@ __global__ void __launch_bounds__(LA_WARPS * 32) linear_attention_scan_kernel(
     int segs_max) {
     pdl_wait();
     pdl_launch_dependents();
+    // q, k and this block's 32 columns of v of LA_STAGE tokens at a time, activation applied once, for all four warps
+    __shared__ float stage[LA_STAGE][2 * LA_MAX_DIM + LA_COLS * LA_WARPS];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int h = blockIdx.y;
     const int seq = MODE == 0 ? blockIdx.x : blockIdx.x / segs_max;
     const int seg = MODE == 0 ? 0 : blockIdx.x % segs_max;
-    const int col0 = (blockIdx.z * LA_WARPS + warp) * LA_COLS;
-    if (col0 >= vdim) return;
+    const int bcol0 = blockIdx.z * LA_WARPS * LA_COLS;  // the block's first column
+    const int col0 = bcol0 + warp * LA_COLS;
+    const bool mine_cols = col0 < vdim;  // a warp beyond the last column only helps to stage
     int row0 = seq_q_start[seq];
     int row1 = seq_q_start[seq + 1];
     bool last = true;
     if (MODE != 0) {
         row0 += seg * seg_len;
-        if (row0 >= row1) return;
+        if (row0 >= row1) return;  // the whole block
         last = row0 + seg_len >= row1;
         if (!last) row1 = row0 + seg_len;
         if (MODE == 1 && last) return;  // nobody starts from the end of the last segment
     }
+    if (row1 <= row0) return;
     const float lam = decay[h];
-    const size_t tile = ((size_t)h * vdim + col0) * dim;
+    const size_t tile = ((size_t)h * vdim + (mine_cols ? col0 : 0)) * dim;
     const size_t per_state = (size_t)heads * vdim * dim;
     float* slot_state = state + (size_t)seq_state_slot[seq] * per_state + tile;
     float* seg_state = MODE == 0 ? slot_state : scratch + (size_t)(row0 / seg_len + seq) * per_state + tile;
@@ -87,45 +94,54 @@ __global__ void __launch_bounds__(LA_WARPS * 32) linear_attention_scan_kernel(
 #pragma unroll
         for (int r = 0; r < RPL; ++r) {
             const int i = lane + 32 * r;
-            S[c][r] = (MODE != 1 && col0 + c < vdim && i < dim) ? seg_state[(size_t)c * dim + i] : 0.0f;
+            S[c][r] = (MODE != 1 && mine_cols && col0 + c < vdim && i < dim) ? seg_state[(size_t)c * dim + i] : 0.0f;
         }
     const int my_col = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
-    for (int t = row0; t < row1; ++t) {
-        const T* row = qkv + (size_t)t * ld;
-        float kk[RPL], qq[RPL], vv[LA_COLS];
-#pragma unroll
-        for (int r = 0; r < RPL; ++r) {
-            const int i = lane + 32 * r;
-            const float a = i < dim ? to_float(row[k_off + h * dim + i]) : 0.0f;
-            kk[r] = silu ? silu_f(a) : a;
-            if (MODE != 1) {
-                const float b = i < dim ? to_float(row[q_off + h * dim + i]) : 0.0f;
-                qq[r] = silu ? silu_f(b) : b;
-            }
+    const int bcols = min(LA_COLS * LA_WARPS, vdim - bcol0);
+    const int per_token = 2 * dim + bcols;  // values to stage per token: k, q, the block's v columns
+    for (int t0 = row0; t0 < row1; t0 += LA_STAGE) {
+        const int nt = min(LA_STAGE, row1 - t0);
+        __syncthreads();  // the tokens staged before have been used
+        for (int w = threadIdx.x; w < nt * per_token; w += LA_WARPS * 32) {
+            const int tt = w / per_token, e = w % per_token;
+            if (MODE == 1 && e >= dim && e < 2 * dim) continue;  // no queries in the pass that only sums
+            const T* row = qkv + (size_t)(t0 + tt) * ld;
+            const int src = e < dim ? k_off + h * dim + e : (e < 2 * dim ? q_off + h * dim + (e - dim) : v_off + h * vdim + bcol0 + (e - 2 * dim));
+            const float a = to_float(row[src]);
+            const int dst = e < dim ? e : (e < 2 * dim ? LA_MAX_DIM + (e - dim) : 2 * LA_MAX_DIM + (e - 2 * dim));
+            stage[tt][dst] = silu ? silu_f(a) : a;
         }
-#pragma unroll
-        for (int c = 0; c < LA_COLS; ++c) {
-            const float a = col0 + c < vdim ? to_float(row[v_off + h * vdim + col0 + c]) : 0.0f;
-            vv[c] = silu ? silu_f(a) : a;
-        }
-        float o[LA_COLS];
-#pragma unroll
-        for (int c = 0; c < LA_COLS; ++c) {
-            float acc = 0.0f;
+        __syncthreads();
+        if (!mine_cols) continue;
+        for (int tt = 0; tt < nt; ++tt) {
+            float kk[RPL], qq[RPL], vv[LA_COLS];
 #pragma unroll
             for (int r = 0; r < RPL; ++r) {
-                S[c][r] = fmaf(kk[r], vv[c], lam * S[c][r]);
-                if (MODE != 1) acc = fmaf(S[c][r], qq[r], acc);
+                const int i = lane + 32 * r;
+                kk[r] = i < dim ? stage[tt][i] : 0.0f;
+                qq[r] = (MODE != 1 && i < dim) ? stage[tt][LA_MAX_DIM + i] : 0.0f;
             }
-            o[c] = acc;
-        }
-        if (MODE != 1) {
-            const float mine = reduce_columns(o, lane);
-            if ((lane & 3) == 0 && col0 + my_col < vdim) out[(size_t)t * ldo + h * vdim + col0 + my_col] = mine;
+#pragma unroll
+            for (int c = 0; c < LA_COLS; ++c) vv[c] = col0 + c < vdim ? stage[tt][2 * LA_MAX_DIM + warp * LA_COLS + c] : 0.0f;
+            float o[LA_COLS];
+#pragma unroll
+            for (int c = 0; c < LA_COLS; ++c) {
+                float acc = 0.0f;
+#pragma unroll
+                for (int r = 0; r < RPL; ++r) {
+                    S[c][r] = fmaf(kk[r], vv[c], lam * S[c][r]);
+                    if (MODE != 1) acc = fmaf(S[c][r], qq[r], acc);
+                }
+                o[c] = acc;
+            }
+            if (MODE != 1) {
+                const float sum = reduce_columns(o, lane);
+                if ((lane & 3) == 0 && col0 + my_col < vdim) out[(size_t)(t0 + tt) * ldo + h * vdim + col0 + my_col] = sum;
+            }
         }
     }
     float* dst = MODE == 1 ? seg_state : slot_state;
-    if (MODE == 1 || (write_state && last)) {
+    if (mine_cols && (MODE == 1 || (write_state && last))) {
 #pragma unroll
         for (int c = 0; c < LA_COLS; ++c)
 #pragma unroll

@@ -648,13 +648,26 @@ def rope_cache_write(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: Optio
     )
 
 
+_attention_tiled = True
+
+
+def set_attention_tiled(on: bool = True) -> None:
+    """Portions of prompts on the general attention's tiled kernel (True, the default) or on the kernel of single
+    tokens (False), for comparisons."""
+    global _attention_tiled
+    _attention_tiled = bool(on)
+
+
 def paged_attention_simt(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                          block_tables: torch.Tensor, token_seq: torch.Tensor, positions: torch.Tensor,
                          num_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float,
-                         score_slopes: Optional[torch.Tensor] = None, v_head_dim: Optional[int] = None):
+                         score_slopes: Optional[torch.Tensor] = None, v_head_dim: Optional[int] = None,
+                         max_q_len: int = 1):
     """General attention over the paged cache; q is read from the first nh*d columns of ``qkv``.
     ``score_slopes`` (fp32 [num_heads]): the score of a query at position P and the key at position j gets
-    slopes[head] * (j - P) added.  ``v_head_dim``: size of a value head where it differs from the keys'."""
+    slopes[head] * (j - P) added.  ``v_head_dim``: size of a value head where it differs from the keys'.
+    ``max_q_len``: the most tokens a request brings; above one (portions of prompts) the kernel that shares tiles of
+    keys among 64 query rows runs where it takes the geometry."""
     dv = int(v_head_dim or head_dim)
     T, _, ldq = _rows(qkv, "attention queries")
     T2, width, ldo = _rows(out, "attention output")
@@ -672,8 +685,13 @@ def paged_attention_simt(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Te
         _need(score_slopes, "score slopes", torch.float32)
         if score_slopes.numel() != num_heads:
             raise KernelError("attention: one score slope per query head is needed")
+    fn = _lib().ferris_paged_attention_simt
+    if max_q_len > 1 and _attention_tiled and (ldq * qkv.element_size()) % 16 == 0 and qkv.data_ptr() % 16 == 0 \
+            and _lib().ferris_paged_attention_tiled_takes(_c_int(_dt(qkv, "attention")), _c_int(num_heads),
+                                                          _c_int(num_kv_heads), _c_int(head_dim), _c_int(dv)):
+        fn = _lib().ferris_paged_attention_tiled
     _check(
-        _lib().ferris_paged_attention_simt(_ptr(qkv), _c_int(ldq), _ptr(out), _c_int(ldo), _ptr(k_cache), _ptr(v_cache),
+        fn(_ptr(qkv), _c_int(ldq), _ptr(out), _c_int(ldo), _ptr(k_cache), _ptr(v_cache),
                                            _dt(qkv, "attention"), _ptr(block_tables), _c_int(block_tables.shape[1]),
                                            _ptr(token_seq), _ptr(positions), _c_int(T), _c_int(num_heads),
                                            _c_int(num_kv_heads), _c_int(head_dim), _c_int(dv), _c_int(k_cache.shape[2]),
@@ -1053,7 +1071,8 @@ def paged_attention(qkv, out, k_cache, v_cache, block_tables, ctx, num_heads, nu
     _need(block_tables, "block tables", torch.int32)
     if v_head_dim is not None and v_head_dim != head_dim:
         paged_attention_simt(qkv, out, k_cache, v_cache, block_tables, ctx.token_seq, ctx.positions, num_heads,
-                             num_kv_heads, head_dim, window, scale, score_slopes=score_slopes, v_head_dim=v_head_dim)
+                             num_kv_heads, head_dim, window, scale, score_slopes=score_slopes, v_head_dim=v_head_dim,
+                             max_q_len=ctx.max_q_len)
         return
     if k_cache.dim() != 4 or k_cache.shape[1] != num_kv_heads or k_cache.shape[3] != head_dim \
             or v_cache.shape != k_cache.shape or block_tables.dim() != 2:
@@ -1062,7 +1081,7 @@ def paged_attention(qkv, out, k_cache, v_cache, block_tables, ctx, num_heads, nu
         raise KernelError(f"attention: q {tuple(qkv.shape)}, out {tuple(out.shape)}")
     if score_slopes is not None or not tensor_core_attention_takes(qkv.dtype, num_heads, num_kv_heads, head_dim, k_cache.shape[2]):
         paged_attention_simt(qkv, out, k_cache, v_cache, block_tables, ctx.token_seq, ctx.positions, num_heads,
-                             num_kv_heads, head_dim, window, scale, score_slopes=score_slopes)
+                             num_kv_heads, head_dim, window, scale, score_slopes=score_slopes, max_q_len=ctx.max_q_len)
         return
     T = qkv.shape[0]
     singles = getattr(ctx, "single_rows", None)

@@ -326,14 +326,55 @@ def test_unit_norm_temperature_slopes_window_attention(device, nh, nkv, d, dv, w
             ops.qk_prepare_cache_write(rows, ctx.positions, slots[pos:pos + n].contiguous(), k, v, nh, nkv, d, dv, 1e-6, (0.4, 5))
             out = torch.empty(n, nh * dv, dtype=dtype, device=device)
             ops.paged_attention_simt(rows, out, k, v, table, ctx.token_seq, ctx.positions, nh, nkv, d, window,
-                                     mixer["scale"], score_slopes=slopes, v_head_dim=dv)
+                                     mixer["scale"], score_slopes=slopes, v_head_dim=dv, max_q_len=n)
             assert torch.allclose(out.cpu().double(), want[pos:pos + n], **tol), (cuts, pos)
+            if n > 1:  # the kernel of single tokens serves portions too, and agrees
+                again = torch.empty_like(out)
+                ops.paged_attention_simt(rows, again, k, v, table, ctx.token_seq, ctx.positions, nh, nkv, d, window,
+                                         mixer["scale"], score_slopes=slopes, v_head_dim=dv, max_q_len=1)
+                assert torch.allclose(again.cpu().double(), want[pos:pos + n], **tol), (cuts, pos)
             pos += n
 
 
+def test_attention_tiles_that_hold_tokens_of_several_requests(device):
+    """One step of four requests (a portion of 37, a single token deep in its sequence, a portion of two, one of 30
+    from position 0), each over pages of its own: the tiled kernel's rows of one tile belong to several requests, and
+    every row equals the kernel of single tokens, which takes rows one by one."""
+    ops = _ops()
+    from ferrisinfer_b200.parts.position import DistanceSlopes
+
+    torch.manual_seed(9)
+    nh, nkv, d, dv, ps, window = 4, 2, 32, 24, 16, 29
+    q_lens, start = [37, 1, 2, 30], [20, 90, 7, 0]
+    total = [a + b for a, b in zip(q_lens, start)]
+    blocks = [-(-n // ps) for n in total]
+    pages = sum(blocks)
+    k = torch.randn(pages + 1, nkv, ps, d, device=device)
+    v = torch.randn(pages + 1, nkv, ps, dv, device=device)
+    order = torch.randperm(pages).tolist()
+    tables = torch.full((4, max(blocks)), -1, dtype=torch.int32)
+    at = 0
+    for i, n in enumerate(blocks):
+        tables[i, :n] = torch.tensor(order[at:at + n], dtype=torch.int32)
+        at += n
+    tables = tables.to(device)
+    S = len(q_lens)
+    ctx = fake_ctx(device, q_lens, start, list(range(S)))
+    T = sum(q_lens)
+    qkv = torch.randn(T, nh * d + nkv * (d + dv), device=device)
+    slopes = DistanceSlopes(8.0).score_slopes(nh, device)
+    tiled, single = torch.empty(T, nh * dv, device=device), torch.empty(T, nh * dv, device=device)
+    for out, longest in ((tiled, max(q_lens)), (single, 1)):
+        ops.paged_attention_simt(qkv, out, k, v, tables, ctx.token_seq, ctx.positions, nh, nkv, d, window, 0.3,
+                                 score_slopes=slopes, v_head_dim=dv, max_q_len=longest)
+    assert torch.isfinite(tiled).all()
+    assert torch.allclose(tiled, single, atol=2e-5, rtol=1e-4)
+
+
+@pytest.mark.parametrize("tiled", [False, True])
 @pytest.mark.parametrize("back,seen", [(0, True), (15, True), (16, True), (31, True), (32, True), (36, True), (37, False),
                                        (48, False)])
-def test_attention_window_edge_one_key_stands_out(device, back, seen):
+def test_attention_window_edge_one_key_stands_out(device, back, seen, tiled):
     """A window of 37 over pages of 16.  The key ``back`` positions before the last query points the query's way and every
     other key the opposite way, so the output is that key's value if (and only if) the window holds it."""
     ops = _ops()
@@ -350,7 +391,8 @@ def test_attention_window_edge_one_key_stands_out(device, back, seen):
     ctx = fake_ctx(device, [T], [0], [0])
     ops.qk_prepare_cache_write(qkv, ctx.positions, slots, k, v, 1, 1, d, d, 1e-6, None)
     out = torch.empty(T, d, device=device)
-    ops.paged_attention_simt(qkv, out, k, v, table, ctx.token_seq, ctx.positions, 1, 1, d, window, 1.0)
+    ops.paged_attention_simt(qkv, out, k, v, table, ctx.token_seq, ctx.positions, 1, 1, d, window, 1.0,
+                             max_q_len=T if tiled else 1)
     # unit norm makes |q| = |k| = sqrt(d): the matching key scores +32, the others -32
     hit = float((out[T - 1].cpu() - values[T - 1 - back]).abs().max()) < 1e-3
     assert hit == seen
