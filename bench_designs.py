@@ -56,21 +56,25 @@ def qwen2_config(s: dict) -> dict:
             "use_sliding_window": True, "sliding_window": WINDOW, "max_window_layers": 0}
 
 
-def _timed(fn, flush, warmup=3, iters=5):
+def _timed(fn, flush, warmup=3, iters=5, reps=1):
+    """Seconds per launch: the median of ``iters`` regions of ``reps`` launches back to back, a buffer larger than L2
+    written before each region.  ``reps`` > 1 for kernels of a few microseconds, whose single launch would be timed
+    together with the host's way to it; their operands are small and lie in L2 inside a step as well."""
     import torch
 
     for _ in range(warmup):
         fn()
     times = []
     for _ in range(iters):
-        flush.add_(1.0)  # write a buffer larger than L2 between timed launches
+        flush.add_(1.0)
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        fn()
+        for _ in range(reps):
+            fn()
         e1.record()
         torch.cuda.synchronize()
-        times.append(e0.elapsed_time(e1))
+        times.append(e0.elapsed_time(e1) / reps)
     return statistics.median(times) * 1e-3
 
 
@@ -135,36 +139,38 @@ def kernel_numbers(s: dict, peaks: dict) -> dict:
         o = torch.empty(T, H * d, dtype=bf, device=dev)
         ctx = ctx_of([q_len] * batch, ctx_len)
         t = _timed(lambda: ops.paged_attention_simt(qkv, o, k, v, tables, ctx.token_seq, ctx.positions, H, G, d, WINDOW,
-                                                    1.0 / math.sqrt(d), score_slopes=slopes, v_head_dim=d), flush)
+                                                    1.0 / math.sqrt(d), score_slopes=slopes, v_head_dim=d,
+                                                    max_q_len=q_len), flush)
         keys = sum(min(WINDOW, ctx_len + j + 1) for j in range(q_len)) * batch
         if q_len == 1:
             record(name, t, bytes_=batch * G * min(WINDOW, ctx_len + 1) * 2 * d * 2 + T * H * d * 4, flops=4.0 * keys * H * d)
         else:
             record(name, t, flops=4.0 * keys * H * d)
         slots = (tables[ctx.token_seq.long(), (ctx.positions // 16).long()] * 16 + ctx.positions % 16).int()
-        t = _timed(lambda: ops.qk_prepare_cache_write(qkv, ctx.positions, slots, k, v, H, G, d, d, 1e-6, (0.3, 128)), flush)
+        t = _timed(lambda: ops.qk_prepare_cache_write(qkv, ctx.positions, slots, k, v, H, G, d, d, 1e-6, (0.3, 128)), flush,
+                   reps=10)
         record(name.replace("window_attention", "qk_prepare"), t, bytes_=T * (2 * H * d + 4 * G * d) * 2)
     # ---- row-wise kernels of a long step and of a decode step
     for tag, T in (("2048", 2048), ("b64", 64)):
         h = torch.randn(T, W, device=dev)
         w1, w2 = torch.ones(W, device=dev), torch.ones(W, device=dev)
         a, b = torch.empty(T, W, dtype=bf, device=dev), torch.empty(T, W, dtype=bf, device=dev)
-        t = _timed(lambda: ops.grouped_rmsnorm_pair(h, w1, w2, 1e-6, 4, a, b), flush)
+        t = _timed(lambda: ops.grouped_rmsnorm_pair(h, w1, w2, 1e-6, 4, a, b), flush, reps=10 if T <= 64 else 1)
         record(f"norm_pair_{tag}", t, bytes_=T * W * (4 + 2 + 2))
         cw = torch.randn(W, 4, device=dev) * 0.1
         cs = torch.zeros(T + 1, 3, W, device=dev)
         ctx = ctx_of([T], 0) if T > 64 else ctx_of([1] * T, 5)
-        t = _timed(lambda: ops.short_conv(a, b, cw, cs, ctx), flush)
+        t = _timed(lambda: ops.short_conv(a, b, cw, cs, ctx), flush, reps=10 if T <= 64 else 1)
         record(f"short_conv_{tag}", t, bytes_=T * W * 4 + (ctx.num_seqs * 3 * W * 8 if T <= 64 else 0))
         z = torch.randn(T, ff, device=dev).to(bf)
         pq = torch.tensor([0.3, -0.2], device=dev)
-        t = _timed(lambda: ops.activation(z, z, "xielu", pq), flush)
+        t = _timed(lambda: ops.activation(z, z, "xielu", pq), flush, reps=10 if T <= 64 else 1)
         record(f"xielu_{tag}", t, bytes_=T * ff * 4)
         o = torch.randn(T, H * d, device=dev)
         g = torch.randn(T, H * d, device=dev).to(bf)
         y = torch.empty(T, H * d, dtype=bf, device=dev)
         nw = torch.ones(H * d, device=dev)
-        t = _timed(lambda: ops.gated_rmsnorm(o, g, nw, 1e-6, y), flush)
+        t = _timed(lambda: ops.gated_rmsnorm(o, g, nw, 1e-6, y), flush, reps=10 if T <= 64 else 1)
         record(f"gated_norm_{tag}", t, bytes_=T * H * d * (4 + 2 + 2))
     return out
 

@@ -281,6 +281,190 @@ __global__ void __launch_bounds__(AL_THREADS)
     }
 }
 
+// Single tokens where several query heads share a kv head: a block takes G of those heads at once, SIXTEEN lanes share
+// a key and hold a sixteenth of it, so a key and its value are read, and widened to fp32, once for the G heads, and
+// each group of sixteen keeps U keys in flight.  What bounds a step of single tokens is the bytes in flight per SM.
+constexpr int AG_THREADS = 128;
+constexpr int AG_GROUPS = AG_THREADS / 16;
+
+template <typename T, int MAXC, int G, int U>
+__global__ void __launch_bounds__(AG_THREADS)
+    paged_attention_shared_kernel(const T* q, int ldq, T* __restrict__ out, int ldo, const T* k_cache, const T* v_cache,
+                                  const int* __restrict__ block_tables, int max_blocks,
+                                  const int* __restrict__ token_seq, const int* __restrict__ positions, int nh, int nkv,
+                                  int d, int dv, int page_size, int window, float scale,
+                                  const float* __restrict__ slopes, int splits, float* __restrict__ partial) {
+    extern __shared__ float smem[];  // per group and head: m, z, acc[dv]
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t = blockIdx.x, h0 = blockIdx.y * G;  // query heads h0 .. h0 + G - 1, all of one kv head
+    const int split = blockIdx.z;
+    const int sub = threadIdx.x & 15, grp = threadIdx.x >> 4;
+    const int hk = h0 / (nh / nkv);
+    const int seq = token_seq[t];
+    const int P = positions[t];
+    const int lo = (window > 0 && P - window + 1 > 0) ? P - window + 1 : 0;
+    const int* table = block_tables + (size_t)seq * max_blocks;
+    const int ch = d >> 4, cv = dv >> 4;
+    const int pshift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
+
+    float qv[G][MAXC], acc[G][MAXC], m[G], z[G], slope[G];
+#pragma unroll
+    for (int a = 0; a < G; ++a) {
+#pragma unroll
+        for (int i = 0; i < MAXC; ++i) qv[a][i] = 0.0f, acc[a][i] = 0.0f;
+        load_chunk<MAXC>(q + (size_t)t * ldq + (size_t)(h0 + a) * d + sub * ch, ch, qv[a]);
+        m[a] = -INFINITY, z[a] = 0.0f;
+        slope[a] = slopes ? slopes[h0 + a] : 0.0f;
+    }
+    // the block's share of the keys lo .. P: with several splits, a run of `span` keys each
+    const int span = (P - lo + splits) / splits;
+    const int first = lo + split * span;
+    const int lastk = min(P, first + span - 1);
+    const int rounds = lastk >= first ? (lastk - first + AG_GROUPS * U) / (AG_GROUPS * U) : 0;
+    for (int it = 0; it < rounds; ++it) {
+        float kk[U][MAXC], vv[U][MAXC];
+        bool ok[U];
+        int jj[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int j = first + (it * U + u) * AG_GROUPS + grp;
+            jj[u] = j;
+            int page = -1;
+            if (j <= lastk) page = table[pshift >= 0 ? (j >> pshift) : (j / page_size)];
+            ok[u] = page >= 0;
+            const int in_page = pshift >= 0 ? (j & (page_size - 1)) : (j % page_size);
+            const size_t row = ((size_t)(ok[u] ? page : 0) * nkv + hk) * page_size + (ok[u] ? in_page : 0);
+#pragma unroll
+            for (int i = 0; i < MAXC; ++i) kk[u][i] = 0.0f, vv[u][i] = 0.0f;
+            if (ok[u]) {
+                load_chunk<MAXC>(k_cache + row * d + sub * ch, ch, kk[u]);
+                load_chunk<MAXC>(v_cache + row * dv + sub * cv, cv, vv[u]);
+            }
+        }
+        float dot[U][G];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int a = 0; a < G; ++a) {
+                float x = 0.0f;
+#pragma unroll
+                for (int i = 0; i < MAXC; ++i) x = fmaf(qv[a][i], kk[u][i], x);
+                dot[u][a] = x;
+            }
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1)
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+#pragma unroll
+                for (int a = 0; a < G; ++a) dot[u][a] += __shfl_xor_sync(0xffffffffu, dot[u][a], o);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (!ok[u]) continue;
+#pragma unroll
+            for (int a = 0; a < G; ++a) {
+                const float s = slopes ? fmaf(slope[a], (float)(jj[u] - P), dot[u][a] * scale) : dot[u][a] * scale;
+                float wgt;
+                if (s > m[a]) {
+                    const float rescale = expf(m[a] - s);
+#pragma unroll
+                    for (int i = 0; i < MAXC; ++i) acc[a][i] *= rescale;
+                    z[a] = z[a] * rescale + 1.0f;
+                    m[a] = s;
+                    wgt = 1.0f;
+                } else {
+                    wgt = expf(s - m[a]);
+                    z[a] += wgt;
+                }
+#pragma unroll
+                for (int i = 0; i < MAXC; ++i) acc[a][i] = fmaf(wgt, vv[u][i], acc[a][i]);
+            }
+        }
+    }
+    const int stride = dv + 2;
+#pragma unroll
+    for (int a = 0; a < G; ++a) {
+        float* mine = smem + (size_t)(grp * G + a) * stride;
+        if (sub == 0) {
+            mine[0] = m[a];
+            mine[1] = z[a];
+        }
+#pragma unroll
+        for (int i = 0; i < MAXC; ++i)
+            if (i < cv) mine[2 + sub * cv + i] = acc[a][i];
+    }
+    __syncthreads();
+    for (int w = threadIdx.x; w < G * dv; w += AG_THREADS) {
+        const int a = w / dv, i = w % dv;
+        float mm = -INFINITY;
+        for (int g2 = 0; g2 < AG_GROUPS; ++g2) mm = fmaxf(mm, smem[(size_t)(g2 * G + a) * stride]);
+        float zz = 0.0f, o = 0.0f;
+        for (int g2 = 0; g2 < AG_GROUPS; ++g2) {
+            const float* e = smem + (size_t)(g2 * G + a) * stride;
+            const float f = e[0] == -INFINITY ? 0.0f : expf(e[0] - mm);
+            zz += e[1] * f;
+            o += e[2 + i] * f;
+        }
+        if (splits == 1) {
+            out[(size_t)t * ldo + (size_t)(h0 + a) * dv + i] = from_float<T>(o / zz);
+        } else {  // the share's maximum, sum and weighted values, for the merge kernel
+            float* e = partial + (((size_t)t * nh + h0 + a) * splits + split) * stride;
+            if (i == 0) e[0] = mm, e[1] = zz;
+            e[2 + i] = o;
+        }
+    }
+}
+
+// out = sum_s o_s e^(m_s - M) / sum_s z_s e^(m_s - M) over the shares of the keys that the kernel above left in `partial`
+// ([tokens, heads, splits, 2 + dv]: maximum, sum, weighted values).  A block per (token, head).
+template <typename T>
+__global__ void __launch_bounds__(128) attention_merge_shares_kernel(const float* partial, T* __restrict__ out, int ldo,
+                                                                     int nh, int dv, int splits) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t = blockIdx.x, h = blockIdx.y;
+    const int stride = dv + 2;
+    const float* base = partial + ((size_t)t * nh + h) * splits * stride;
+    float mm = -INFINITY;
+    for (int s2 = 0; s2 < splits; ++s2) mm = fmaxf(mm, base[(size_t)s2 * stride]);
+    float zz = 0.0f;
+    for (int s2 = 0; s2 < splits; ++s2) {
+        const float ms = base[(size_t)s2 * stride];
+        zz += ms == -INFINITY ? 0.0f : base[(size_t)s2 * stride + 1] * expf(ms - mm);
+    }
+    const float inv = 1.0f / zz;
+    for (int i = threadIdx.x; i < dv; i += blockDim.x) {
+        float o = 0.0f;
+        for (int s2 = 0; s2 < splits; ++s2) {
+            const float ms = base[(size_t)s2 * stride];
+            if (ms != -INFINITY) o += base[(size_t)s2 * stride + 2 + i] * expf(ms - mm);
+        }
+        out[(size_t)t * ldo + (size_t)h * dv + i] = from_float<T>(o * inv);
+    }
+}
+
+template <typename T, int G>
+void launch_shared(const void* q, int ldq, void* out, int ldo, const void* k_cache, const void* v_cache,
+                   const int* block_tables, int max_blocks, const int* token_seq, const int* positions, int tokens, int nh,
+                   int nkv, int d, int dv, int page_size, int window, float scale, const float* slopes, int splits,
+                   float* partial, cudaStream_t s) {
+    const dim3 grid(tokens, nh / G, splits), block(AG_THREADS);
+    const size_t smem = (size_t)AG_GROUPS * G * (dv + 2) * sizeof(float);
+    const int most = d > dv ? d : dv;
+#define FERRIS_AG_LAUNCH(MAXC, U)                                                                                       \
+    ferris_launch(paged_attention_shared_kernel<T, MAXC, G, U>, grid, block, smem, s, (const T*)q, ldq, (T*)out, ldo,   \
+                  (const T*)k_cache, (const T*)v_cache, block_tables, max_blocks, token_seq, positions, nh, nkv, d, dv,  \
+                  page_size, window, scale, slopes, splits, partial)
+    if (most <= 128)
+        FERRIS_AG_LAUNCH(8, 4);
+    else
+        FERRIS_AG_LAUNCH(16, 2);
+#undef FERRIS_AG_LAUNCH
+    if (splits > 1)
+        ferris_launch(attention_merge_shares_kernel<T>, dim3(tokens, nh), dim3(128), 0, s, (const float*)partial, (T*)out,
+                      ldo, nh, dv, splits);
+}
+
 template <typename T>
 void launch_lanes(const void* q, int ldq, void* out, int ldo, const void* k_cache, const void* v_cache,
                   const int* block_tables, int max_blocks, const int* token_seq, const int* positions, int tokens, int nh,
@@ -303,8 +487,8 @@ void launch_lanes(const void* q, int ldq, void* out, int ldo, const void* k_cach
 
 
 // ---------------------------------------------------------------------------------------------
-// Portions of prompts: a block takes TL_ROWS = 64 query rows that share their keys and values, namely the g query heads
-// of one kv head for 64 / g consecutive tokens of the step, and walks the keys those tokens see in tiles of 32, which
+// Portions of prompts: a block takes up to TL_ROWS = 64 query rows that share their keys and values, namely the g query
+// heads of one kv head for floor(64 / g) consecutive tokens of the step (rows beyond those stay idle), and walks the keys those tokens see in tiles of 32, which
 // it brings into shared memory once for all 64 rows (fp32, a row's 16-byte pieces spread over the banks).  Eight
 // lanes share two rows: each forms 2 x 4 scores of a tile from shared memory, the eight exchange the rows' maxima
 // and sums by shuffles, write the weights to shared memory and add 2 x (dv / 8) columns of weighted values each.
@@ -506,7 +690,7 @@ size_t tiled_smem_bytes(int d, int dv) {
 bool tiled_takes(int dtype, int nh, int nkv, int d, int dv) {
     const int g = nkv > 0 ? nh / nkv : 0;
     const int unit = dtype == FERRIS_F32 ? 4 : 8;  // elements of a 16-byte piece
-    return g >= 1 && g <= TL_ROWS && (g & (g - 1)) == 0 && nh % nkv == 0 && d % unit == 0 && dv % unit == 0 && d <= 256 &&
+    return g >= 1 && g <= TL_ROWS && nh % nkv == 0 && d % unit == 0 && dv % unit == 0 && d <= 256 &&
            dv <= 256 && tiled_smem_bytes(d, dv) <= 200 * 1024;
 }
 
@@ -541,7 +725,7 @@ FERRIS_API int ferris_paged_attention_simt(const void* q, int ldq, void* out, in
                                            const void* v_cache, int dtype, const int* block_tables, int max_blocks,
                                            const int* token_seq, const int* positions, int tokens, int nh, int nkv,
                                            int d, int dv, int page_size, int window, float scale, const float* slopes,
-                                           void* stream) {
+                                           int kv_span, float* scratch, long long scratch_floats, void* stream) {
     if (tokens <= 0) return FERRIS_OK;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0) FERRIS_REFUSE("attention: %d heads over %d kv heads", nh, nkv);
     if (d <= 0 || d > 32 * MAX_PER_LANE) FERRIS_REFUSE("attention: head size %d not in 1..%d", d, 32 * MAX_PER_LANE);
@@ -555,6 +739,39 @@ FERRIS_API int ferris_paged_attention_simt(const void* q, int ldq, void* out, in
     // head sizes that eight lanes can share evenly, rows that start on 16 bytes: the kernel with eight lanes to a key
     const size_t elt = dtype == FERRIS_F32 ? 4 : 2;
     const bool aligned = (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) == 0 && ((size_t)ldq * elt) % 16 == 0;
+    // Query heads that share keys, where the caller brings scratch for shares of the keys (a step of single tokens):
+    // the keys of a token are cut into as many shares as fill the SMs about three times over, of 64 keys at least.
+    const int g = nh / nkv;
+    if (scratch && kv_span > 0 && g % 2 == 0 && d % 16 == 0 && dv % 16 == 0 && d <= 256 && dv <= 256 && aligned) {
+        const bool four = g % 4 == 0;
+        const long long blocks = (long long)tokens * (nh / (four ? 4 : 2));
+        static int sms = 0;
+        if (sms <= 0) {
+            int dev = 0;
+            cudaGetDevice(&dev);
+            if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+        }
+        // (with enough tokens and heads to fill the SMs four times over as they are, the kernel with a block per token
+        // and head below is faster: a round of this one forms G x U scores per lane and is long.  1B-like sizes, a step
+        // of 8 / 64 single tokens over 1,024 keys: 0.97 / 2.17 ms a step with shares, 1.13 / 1.92 ms without)
+        long long splits = (long long)tokens * nh >= 4LL * sms ? 0 : (3LL * sms + blocks - 1) / blocks;
+        const long long most = kv_span / 64 > 0 ? kv_span / 64 : 1;
+        if (splits > most) splits = most;
+        if (splits > 16) splits = 16;
+        const long long fit = scratch_floats / ((long long)tokens * nh * (dv + 2));
+        if (splits > fit) splits = fit;
+        if (splits >= 1) {
+            const int sp = (int)splits;
+            if (dtype == FERRIS_F32) {
+                if (four) launch_shared<float, 4>(q, ldq, out, ldo, k_cache, v_cache, block_tables, max_blocks, token_seq, positions, tokens, nh, nkv, d, dv, page_size, window, scale, slopes, sp, scratch, s);
+                else launch_shared<float, 2>(q, ldq, out, ldo, k_cache, v_cache, block_tables, max_blocks, token_seq, positions, tokens, nh, nkv, d, dv, page_size, window, scale, slopes, sp, scratch, s);
+            } else {
+                if (four) launch_shared<bf16, 4>(q, ldq, out, ldo, k_cache, v_cache, block_tables, max_blocks, token_seq, positions, tokens, nh, nkv, d, dv, page_size, window, scale, slopes, sp, scratch, s);
+                else launch_shared<bf16, 2>(q, ldq, out, ldo, k_cache, v_cache, block_tables, max_blocks, token_seq, positions, tokens, nh, nkv, d, dv, page_size, window, scale, slopes, sp, scratch, s);
+            }
+            FERRIS_LAUNCH_CHECK();
+        }
+    }
     if (d % 8 == 0 && dv % 8 == 0 && aligned && (size_t)AL_GROUPS * (dv + 2) * sizeof(float) <= 48 * 1024) {
         if (dtype == FERRIS_F32)
             launch_lanes<float>(q, ldq, out, ldo, k_cache, v_cache, block_tables, max_blocks, token_seq, positions, tokens, nh, nkv, d, dv, page_size, window, scale, slopes, s);
@@ -573,8 +790,8 @@ FERRIS_API int ferris_paged_attention_simt(const void* q, int ldq, void* out, in
     FERRIS_LAUNCH_CHECK();
 }
 
-// Whether ferris_paged_attention_tiled takes a geometry (head sizes in 16-byte pieces, a group of query heads that is
-// a power of two and at most 64).
+// Whether ferris_paged_attention_tiled takes a geometry (head sizes in 16-byte pieces, at most 64 query heads to a
+// kv head).
 FERRIS_API int ferris_paged_attention_tiled_takes(int dtype, int nh, int nkv, int d, int dv) {
     return tiled_takes(dtype, nh, nkv, d, dv) ? 1 : 0;
 }

@@ -98,18 +98,25 @@ __global__ void __launch_bounds__(LA_WARPS * 32) linear_attention_scan_kernel(
         }
     const int my_col = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
     const int bcols = min(LA_COLS * LA_WARPS, vdim - bcol0);
-    const int per_token = 2 * dim + bcols;  // values to stage per token: k, q, the block's v columns
     for (int t0 = row0; t0 < row1; t0 += LA_STAGE) {
         const int nt = min(LA_STAGE, row1 - t0);
         __syncthreads();  // the tokens staged before have been used
-        for (int w = threadIdx.x; w < nt * per_token; w += LA_WARPS * 32) {
-            const int tt = w / per_token, e = w % per_token;
-            if (MODE == 1 && e >= dim && e < 2 * dim) continue;  // no queries in the pass that only sums
+        for (int tt = warp; tt < nt; tt += LA_WARPS) {  // a warp per token
             const T* row = qkv + (size_t)(t0 + tt) * ld;
-            const int src = e < dim ? k_off + h * dim + e : (e < 2 * dim ? q_off + h * dim + (e - dim) : v_off + h * vdim + bcol0 + (e - 2 * dim));
-            const float a = to_float(row[src]);
-            const int dst = e < dim ? e : (e < 2 * dim ? LA_MAX_DIM + (e - dim) : 2 * LA_MAX_DIM + (e - 2 * dim));
-            stage[tt][dst] = silu ? silu_f(a) : a;
+            for (int e = lane; e < dim; e += 32) {
+                const float a = to_float(row[k_off + h * dim + e]);
+                stage[tt][e] = silu ? silu_f(a) : a;
+            }
+            if (MODE != 1) {  // no queries in the pass that only sums
+                for (int e = lane; e < dim; e += 32) {
+                    const float a = to_float(row[q_off + h * dim + e]);
+                    stage[tt][LA_MAX_DIM + e] = silu ? silu_f(a) : a;
+                }
+            }
+            for (int e = lane; e < bcols; e += 32) {
+                const float a = to_float(row[v_off + h * vdim + bcol0 + e]);
+                stage[tt][2 * LA_MAX_DIM + e] = silu ? silu_f(a) : a;
+            }
         }
         __syncthreads();
         if (!mine_cols) continue;

@@ -649,6 +649,7 @@ def rope_cache_write(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: Optio
 
 
 _attention_tiled = True
+ATTENTION_MAX_SHARES = 16  # most shares that the keys of a single token are cut into
 
 
 def set_attention_tiled(on: bool = True) -> None:
@@ -662,12 +663,14 @@ def paged_attention_simt(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Te
                          block_tables: torch.Tensor, token_seq: torch.Tensor, positions: torch.Tensor,
                          num_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float,
                          score_slopes: Optional[torch.Tensor] = None, v_head_dim: Optional[int] = None,
-                         max_q_len: int = 1):
+                         max_q_len: int = 1, max_kv_len: int = 0, workspace=None):
     """General attention over the paged cache; q is read from the first nh*d columns of ``qkv``.
     ``score_slopes`` (fp32 [num_heads]): the score of a query at position P and the key at position j gets
     slopes[head] * (j - P) added.  ``v_head_dim``: size of a value head where it differs from the keys'.
     ``max_q_len``: the most tokens a request brings; above one (portions of prompts) the kernel that shares tiles of
-    keys among 64 query rows runs where it takes the geometry."""
+    keys among 64 query rows runs where it takes the geometry.  ``max_kv_len`` and ``workspace`` (a step of single
+    tokens): the most keys a request holds, and where scratch comes from; the keys of a token are then cut into
+    shares that run side by side, and query heads of one kv head share its keys."""
     dv = int(v_head_dim or head_dim)
     T, _, ldq = _rows(qkv, "attention queries")
     T2, width, ldo = _rows(out, "attention output")
@@ -686,17 +689,24 @@ def paged_attention_simt(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Te
         if score_slopes.numel() != num_heads:
             raise KernelError("attention: one score slope per query head is needed")
     fn = _lib().ferris_paged_attention_simt
+    extra = (_c_int(0), _ptr(None), ctypes.c_longlong(0))
+    if max_q_len <= 1 and max_kv_len > 0 and workspace is not None:
+        span = min(max_kv_len, window) if window else max_kv_len
+        floats = T * num_heads * ATTENTION_MAX_SHARES * (dv + 2)
+        scratch = workspace.get("attn_shares", (floats,), torch.float32)
+        extra = (_c_int(span), _ptr(scratch), ctypes.c_longlong(floats))
     if max_q_len > 1 and _attention_tiled and (ldq * qkv.element_size()) % 16 == 0 and qkv.data_ptr() % 16 == 0 \
             and _lib().ferris_paged_attention_tiled_takes(_c_int(_dt(qkv, "attention")), _c_int(num_heads),
                                                           _c_int(num_kv_heads), _c_int(head_dim), _c_int(dv)):
         fn = _lib().ferris_paged_attention_tiled
+        extra = ()
     _check(
         fn(_ptr(qkv), _c_int(ldq), _ptr(out), _c_int(ldo), _ptr(k_cache), _ptr(v_cache),
                                            _dt(qkv, "attention"), _ptr(block_tables), _c_int(block_tables.shape[1]),
                                            _ptr(token_seq), _ptr(positions), _c_int(T), _c_int(num_heads),
                                            _c_int(num_kv_heads), _c_int(head_dim), _c_int(dv), _c_int(k_cache.shape[2]),
-                                           _c_int(window or 0), _c_float(scale), _ptr(score_slopes), _stream()),
-        "paged attention",
+                                           _c_int(window or 0), _c_float(scale), _ptr(score_slopes), *extra, _stream()),
+        "paged attention", 2 if extra and extra[0].value > 0 else 1,
     )
 
 
@@ -1072,7 +1082,7 @@ def paged_attention(qkv, out, k_cache, v_cache, block_tables, ctx, num_heads, nu
     if v_head_dim is not None and v_head_dim != head_dim:
         paged_attention_simt(qkv, out, k_cache, v_cache, block_tables, ctx.token_seq, ctx.positions, num_heads,
                              num_kv_heads, head_dim, window, scale, score_slopes=score_slopes, v_head_dim=v_head_dim,
-                             max_q_len=ctx.max_q_len)
+                             max_q_len=ctx.max_q_len, max_kv_len=ctx.max_kv_len, workspace=ctx.workspace)
         return
     if k_cache.dim() != 4 or k_cache.shape[1] != num_kv_heads or k_cache.shape[3] != head_dim \
             or v_cache.shape != k_cache.shape or block_tables.dim() != 2:
@@ -1081,7 +1091,8 @@ def paged_attention(qkv, out, k_cache, v_cache, block_tables, ctx, num_heads, nu
         raise KernelError(f"attention: q {tuple(qkv.shape)}, out {tuple(out.shape)}")
     if score_slopes is not None or not tensor_core_attention_takes(qkv.dtype, num_heads, num_kv_heads, head_dim, k_cache.shape[2]):
         paged_attention_simt(qkv, out, k_cache, v_cache, block_tables, ctx.token_seq, ctx.positions, num_heads,
-                             num_kv_heads, head_dim, window, scale, score_slopes=score_slopes, max_q_len=ctx.max_q_len)
+                             num_kv_heads, head_dim, window, scale, score_slopes=score_slopes, max_q_len=ctx.max_q_len,
+                             max_kv_len=ctx.max_kv_len, workspace=ctx.workspace)
         return
     T = qkv.shape[0]
     singles = getattr(ctx, "single_rows", None)

@@ -292,7 +292,8 @@ def paged(device, dtype, T, nkv, d, dv, page_size, order):
     return k, v, table, slots
 
 
-@pytest.mark.parametrize("nh,nkv,d,dv,window", [(4, 2, 32, 32, 21), (3, 1, 40, 24, 16), (2, 2, 16, 72, 50), (6, 3, 96, 96, 33)])
+@pytest.mark.parametrize("nh,nkv,d,dv,window", [(4, 2, 32, 32, 21), (3, 1, 40, 24, 16), (2, 2, 16, 72, 50), (6, 3, 96, 96, 33),
+                                                (5, 1, 8, 8, 64), (12, 2, 64, 32, 40)])
 @pytest.mark.parametrize("dtype", [F32, BF16])
 def test_unit_norm_temperature_slopes_window_attention(device, nh, nkv, d, dv, window, dtype):
     """q/k preparation + cache write + attention against the plain attention mixer (identity output matrix), over
@@ -334,6 +335,42 @@ def test_unit_norm_temperature_slopes_window_attention(device, nh, nkv, d, dv, w
                                          mixer["scale"], score_slopes=slopes, v_head_dim=dv, max_q_len=1)
                 assert torch.allclose(again.cpu().double(), want[pos:pos + n], **tol), (cuts, pos)
             pos += n
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("nh,nkv,d,dv", [(8, 2, 64, 64), (4, 2, 96, 32), (6, 1, 16, 16)])
+def test_attention_of_single_tokens_in_shares_of_keys(device, nh, nkv, d, dv, dtype):
+    """Single tokens of three requests, hundreds of keys deep: with scratch from a workspace the keys of a token are
+    cut into shares that run side by side and query heads of a kv head share its keys; the result is that of the
+    kernel that takes a token's keys in one go."""
+    ops = _ops()
+    from ferrisinfer_b200.engine.workspace import Workspace
+    from ferrisinfer_b200.parts.position import DistanceSlopes
+
+    torch.manual_seed(nh + d)
+    ps, window = 16, 260
+    held = [401, 77, 300]  # keys each request holds, its own token included
+    blocks = [-(-n // ps) for n in held]
+    pages = sum(blocks)
+    k = torch.randn(pages + 1, nkv, ps, d, device=device).to(dtype)
+    v = torch.randn(pages + 1, nkv, ps, dv, device=device).to(dtype)
+    tables = torch.full((3, max(blocks)), -1, dtype=torch.int32)
+    order, at = torch.randperm(pages).tolist(), 0
+    for i, n in enumerate(blocks):
+        tables[i, :n] = torch.tensor(order[at:at + n], dtype=torch.int32)
+        at += n
+    tables = tables.to(device)
+    ctx = fake_ctx(device, [1, 1, 1], [n - 1 for n in held], [0, 1, 2])
+    qkv = torch.randn(3, nh * d + nkv * (d + dv), device=device).to(dtype)
+    slopes = DistanceSlopes(8.0).score_slopes(nh, device)
+    whole, shares = torch.empty(3, nh * dv, dtype=dtype, device=device), torch.empty(3, nh * dv, dtype=dtype, device=device)
+    ops.paged_attention_simt(qkv, whole, k, v, tables, ctx.token_seq, ctx.positions, nh, nkv, d, window, 0.2,
+                             score_slopes=slopes, v_head_dim=dv)
+    ops.paged_attention_simt(qkv, shares, k, v, tables, ctx.token_seq, ctx.positions, nh, nkv, d, window, 0.2,
+                             score_slopes=slopes, v_head_dim=dv, max_kv_len=max(held), workspace=Workspace(device))
+    tol = dict(atol=2e-5, rtol=1e-4) if dtype == F32 else dict(atol=2e-2, rtol=2e-2)
+    assert torch.isfinite(shares.float()).all()
+    assert torch.allclose(shares.float(), whole.float(), **tol)
 
 
 def test_attention_tiles_that_hold_tokens_of_several_requests(device):
