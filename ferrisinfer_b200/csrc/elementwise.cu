@@ -509,21 +509,64 @@ __global__ void activation_kernel(const T* in, T* out, long long n, int kind,
     }
 }
 
+// The same, sixteen bytes a thread at a time (eight bf16 values or four floats), where the count and the addresses allow.
+__device__ __forceinline__ float activation_value(float z, int kind, float a, float b) {
+    if (kind == 0) return z > 0.0f ? fmaf(a * z, z, 0.5f * z) : fmaf(b, expm1f(z) - z, 0.5f * z);
+    return z / (1.0f + expf(-z));
+}
+
+template <typename T>
+__global__ void activation_vec_kernel(const uint4* in, uint4* out, long long n16, int kind, const float* __restrict__ params) {
+    pdl_wait();
+    pdl_launch_dependents();
+    float a = 0.0f, b = 0.0f;
+    if (kind == 0) {
+        a = softplus_f(params[0]);
+        b = 0.5f + softplus_f(params[1]);
+    }
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (long long)gridDim.x * blockDim.x) {
+        uint4 u = in[i];
+        uint32_t* w = reinterpret_cast<uint32_t*>(&u);
+        if (sizeof(T) == 4) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) w[k] = __float_as_uint(activation_value(__uint_as_float(w[k]), kind, a, b));
+        } else {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float lo = activation_value(__uint_as_float(w[k] << 16), kind, a, b);
+                const float hi = activation_value(__uint_as_float(w[k] & 0xffff0000u), kind, a, b);
+                const __nv_bfloat162 pair = __floats2bfloat162_rn(lo, hi);
+                w[k] = *reinterpret_cast<const uint32_t*>(&pair);
+            }
+        }
+        out[i] = u;
+    }
+}
+
 FERRIS_API int ferris_activation(const void* in, void* out, int dtype, long long n, int kind, const float* params,
                                  void* stream) {
     if (n <= 0) return FERRIS_OK;
     if (kind < 0 || kind > 1) FERRIS_REFUSE("activation: unknown kind %d", kind);
     if (kind == 0 && !params) FERRIS_REFUSE("activation: xIELU needs its two numbers");
+    if (dtype != FERRIS_F32 && dtype != FERRIS_BF16) FERRIS_REFUSE("activation: unknown dtype %d", dtype);
     const int threads = 256;
+    cudaStream_t s = (cudaStream_t)stream;
+    const long long per16 = dtype == FERRIS_F32 ? 4 : 8;
+    if (n % per16 == 0 && (((uintptr_t)in | (uintptr_t)out) & 15) == 0) {
+        const long long n16 = n / per16, want = (n16 + threads - 1) / threads;
+        const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+        if (dtype == FERRIS_F32)
+            ferris_launch(activation_vec_kernel<float>, dim3(blocks), dim3(threads), 0, s, (const uint4*)in, (uint4*)out, n16, kind, params);
+        else
+            ferris_launch(activation_vec_kernel<bf16>, dim3(blocks), dim3(threads), 0, s, (const uint4*)in, (uint4*)out, n16, kind, params);
+        FERRIS_LAUNCH_CHECK();
+    }
     const long long want = (n + threads - 1) / threads;
     const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
-    cudaStream_t s = (cudaStream_t)stream;
     if (dtype == FERRIS_F32)
         ferris_launch(activation_kernel<float>, dim3(blocks), dim3(threads), 0, s, (const float*)in, (float*)out, n, kind, params);
-    else if (dtype == FERRIS_BF16)
-        ferris_launch(activation_kernel<bf16>, dim3(blocks), dim3(threads), 0, s, (const bf16*)in, (bf16*)out, n, kind, params);
     else
-        FERRIS_REFUSE("activation: unknown dtype %d", dtype);
+        ferris_launch(activation_kernel<bf16>, dim3(blocks), dim3(threads), 0, s, (const bf16*)in, (bf16*)out, n, kind, params);
     FERRIS_LAUNCH_CHECK();
 }
 

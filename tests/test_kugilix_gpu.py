@@ -268,10 +268,11 @@ def test_gated_rmsnorm(device, dtype):
     assert torch.allclose(out.double(), want, atol=tol, rtol=tol)
 
 
+@pytest.mark.parametrize("n", [1001, 4096])  # one value a thread; sixteen bytes a thread
 @pytest.mark.parametrize("dtype", [F32, BF16])
-def test_xielu_activation(device, dtype):
+def test_xielu_activation(device, dtype, n):
     ops = _ops()
-    z = torch.linspace(-9, 9, 1001, device=device).to(dtype)
+    z = torch.linspace(-9, 9, n, device=device).to(dtype)
     params = torch.tensor([0.4, -1.1], device=device)
     out = torch.empty_like(z)
     ops.activation(z, out, "xielu", params)
