@@ -66,13 +66,19 @@ struct SkParams {
     int up_row_offset;
     int mode;
     int* status;
+    FerrisEpilogueAct act;  // the ACT instance only
 };
 
 __device__ __forceinline__ float sk_silu_mul(float g, float u) { return u * (g * (1.0f / (1.0f + expf(-g)))); }
 
 // a: the product (the gate's in SwiGLU mode), b: the up product, bias_v: bias[n] or 0, old: what out[t, n] held.
+// ACT: the instance that applies the epilogue's activation before its bf16 store (a kernel of its own, so that the
+// others are the code they were).
+template <bool ACT>
 __device__ __forceinline__ void sk_write(const SkParams& p, int t, int n, float a, float b, float bias_v, float old) {
-    if (p.mode == SK_STORE_BF16) {
+    if (ACT) {
+        reinterpret_cast<bf16*>(p.out)[(size_t)t * p.ldo + n] = __float2bfloat16_rn(ferris_epilogue_act(a + bias_v, p.act));
+    } else if (p.mode == SK_STORE_BF16) {
         reinterpret_cast<bf16*>(p.out)[(size_t)t * p.ldo + n] = __float2bfloat16_rn(a + bias_v);
     } else if (p.mode == SK_STORE_F32) {
         reinterpret_cast<float*>(p.out)[(size_t)t * p.ldo + n] = a + bias_v;
@@ -85,7 +91,7 @@ __device__ __forceinline__ void sk_write(const SkParams& p, int t, int n, float 
 
 // ACCS: 2 in SwiGLU mode (gate rows and up rows of the same outputs), else 1.  NT: 8-token tiles (1 or 2).
 // Shared memory: the weight stages (a ring when the slab does not fit), then the step's rows, one box per K block.
-template <int ACCS, int NT>
+template <int ACCS, int NT, bool ACT = false>
 __global__ void __launch_bounds__(SK_THREADS, 1)
     gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                        const SkParams p) {
@@ -379,7 +385,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1)
             va += red[(size_t)(w * per_warp + e) * 32 + ln];
             if (ACCS == 2) vb += red[(size_t)(w * per_warp + per_acc + e) * 32 + ln];
         }
-        sk_write(p, out_t[i], out_n[i], va, vb, bias_r[i], old_r[i]);
+        sk_write<ACT>(p, out_t[i], out_n[i], va, vb, bias_r[i], old_r[i]);
     }
     FERRIS_TL_MARK(tl_mark, 4);
     FERRIS_TL_END(40 + p.mode + (p.norm_h ? 4 : 0));
@@ -488,11 +494,11 @@ bool sk_plan(int T, int N, int K, int accs, bool rows_by_tma, SkPlan* out) {
     return true;
 }
 
-template <int ACCS, int NT>
+template <int ACCS, int NT, bool ACT = false>
 int sk_launch(const CUtensorMap& mw, const CUtensorMap& mx, const SkParams& p, int ctas, size_t smem, cudaStream_t s) {
-    int rc = ferris_allow_dynamic_smem((const void*)gemm_skinny_kernel<ACCS, NT>, smem);
+    int rc = ferris_allow_dynamic_smem((const void*)gemm_skinny_kernel<ACCS, NT, ACT>, smem);
     if (rc != FERRIS_OK) return rc;
-    cudaError_t e = ferris_launch(gemm_skinny_kernel<ACCS, NT>, dim3(ctas), dim3(SK_THREADS), smem, s, mw, mx, p);
+    cudaError_t e = ferris_launch(gemm_skinny_kernel<ACCS, NT, ACT>, dim3(ctas), dim3(SK_THREADS), smem, s, mw, mx, p);
     if (e != cudaSuccess) {
         ferris_set_error("skinny gemm: %s", cudaGetErrorString(e));
         return (int)e;
@@ -532,6 +538,8 @@ FERRIS_API int ferris_gemm_skinny(const void* x, int ldx, const float* norm_h, c
                                   int ldo, int rows_w, int up_row_offset, void* stream) {
     if (T <= 0 || N <= 0) return FERRIS_OK;
     if (mode < 0 || mode > 3) FERRIS_REFUSE("skinny gemm: unknown mode %d", mode);
+    const FerrisEpilogueAct act = ferris_take_epilogue_act();
+    if (act.kind && mode != SK_STORE_BF16) FERRIS_REFUSE("skinny gemm: an activation goes with the bf16 store, not mode %d", mode);
     const int accs = mode == SK_SWIGLU_BF16 ? 2 : 1;
     SkPlan plan;
     if (!sk_plan(T, N, K, accs, norm_h == nullptr, &plan))
@@ -586,9 +594,12 @@ FERRIS_API int ferris_gemm_skinny(const void* x, int ldx, const float* norm_h, c
     p.up_row_offset = up_row_offset;
     p.mode = mode;
     p.status = ferris_status_ptr();
+    p.act = act;
     cudaStream_t s = (cudaStream_t)stream;
     if (accs == 2)
         return T > 8 ? sk_launch<2, 2>(mw, mx, p, plan.ctas, plan.smem, s) : sk_launch<2, 1>(mw, mx, p, plan.ctas, plan.smem, s);
+    if (act.kind)
+        return T > 8 ? sk_launch<1, 2, true>(mw, mx, p, plan.ctas, plan.smem, s) : sk_launch<1, 1, true>(mw, mx, p, plan.ctas, plan.smem, s);
     return T > 8 ? sk_launch<1, 2>(mw, mx, p, plan.ctas, plan.smem, s) : sk_launch<1, 1>(mw, mx, p, plan.ctas, plan.smem, s);
 }
 

@@ -682,6 +682,7 @@ struct PTParams {
     int up_row_offset;
     int* status;
     RopeEpilogue rope;  // mode QKV_ROPE_BF16 only
+    FerrisEpilogueAct act;  // applied by the bf16 store (mode STORE_BF16)
 };
 
 // The epilogue of one q/k/v tile for one warp: its 32 tokens (lane = token t) and every second item of 64
@@ -805,6 +806,7 @@ __device__ __forceinline__ void pt_epilogue_tile(const PTParams& p, const CUtens
                 } else {
                     v0 = __uint_as_float(ra[c]) + ((p.bias && n + c < p.N) ? __ldg(p.bias + n + c) : 0.0f);
                     v1 = __uint_as_float(ra[c + 1]) + ((p.bias && n + c + 1 < p.N) ? __ldg(p.bias + n + c + 1) : 0.0f);
+                    if (p.act.kind) v0 = ferris_epilogue_act(v0, p.act), v1 = ferris_epilogue_act(v1, p.act);
                 }
                 packed[c >> 1] = pack_bf16(v0, v1);
             }
@@ -1459,6 +1461,11 @@ struct TokenSource {
     int merge_splits = 0, merge_heads = 0, merge_d = 0;
 };
 
+// Whether a bf16-storing product of these sizes runs a kernel that applies an activation in its epilogue.
+FERRIS_API int ferris_gemm_tcgen05_fuses_activation(int T, int N, int K, int ldo, const void* out) {
+    return token_major_pays(0 /* STORE_BF16 */, T, N, K) && ((size_t)ldo * 2) % 16 == 0 && ((uintptr_t)out & 15) == 0 ? 1 : 0;
+}
+
 static int gemm_tcgen05_impl(const void* x, const void* w, const float* bias, void* out, int mode, int T, int N, int K,
                              int ldx, int ldw, int ldo, int rows_w, int up_row_offset, float* scratch, int* counters,
                              void* stream, const TokenSource& src);
@@ -1509,6 +1516,12 @@ FERRIS_API int ferris_merge_gemm_tcgen05(const float* scratch_parts, int heads, 
     return gemm_tcgen05_impl(w, w, bias, out, mode, T, N, K, K, ldw, ldo, rows_w, 0, nullptr, nullptr, stream, src);
 }
 
+// The activation that the product being launched applies in its bf16 store (taken from ferris_gemm_set_activation at
+// the entry of the launcher; none for every other mode).  Only the kernels of long steps apply one: their epilogue
+// tests it once per 32 columns, while the kernel of short steps is measurably slower for any test in its epilogue
+// (a decode step of 1 / 8 / 64 rows at the 0.5B sizes: 0.751 / 0.757 / 1.673 ms with one, 0.725 / 0.752 / 1.64 ms without).
+static FerrisEpilogueAct g_launch_act = {0, 0.0f, 0.0f};
+
 // The persistent token-major kernel for a long step (T >= 128 tokens; output rows aligned for 16-byte stores).
 static int run_tokens_m(const void* x, const void* w, const float* bias, void* out, int mode, int T, int N, int K,
                         int ldx, int ldw, int ldo, int rows_w, int up_row_offset, const RopeEpilogue* rope,
@@ -1519,6 +1532,7 @@ static int run_tokens_m(const void* x, const void* w, const float* bias, void* o
     PTParams q;
     q.out = out;
     q.bias = bias;
+    q.act = g_launch_act;
     q.T = T;
     q.N = N;
     q.K = K;
@@ -1580,6 +1594,9 @@ static int gemm_tcgen05_impl(const void* x, const void* w, const float* bias, vo
         FERRIS_REFUSE("tensor-core gemm: K=%d and row strides %d, %d must be multiples of 8 elements", K, ldx, ldw);
     if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) FERRIS_REFUSE("tensor-core gemm: operands must be 16-byte aligned");
     if (mode < 0 || mode > 3) FERRIS_REFUSE("tensor-core gemm: unknown mode %d", mode);
+    g_launch_act = ferris_take_epilogue_act();
+    if (g_launch_act.kind && mode != STORE_BF16)
+        FERRIS_REFUSE("tensor-core gemm: an activation goes with the bf16 store, not mode %d", mode);
     if (mode == SWIGLU_BF16 && (bias || up_row_offset + N > rows_w)) FERRIS_REFUSE("tensor-core gemm: bad SwiGLU operands");
     if (mode != SWIGLU_BF16 && N > rows_w) FERRIS_REFUSE("tensor-core gemm: %d outputs from %d weight rows", N, rows_w);
     if (ldo < N) FERRIS_REFUSE("tensor-core gemm: output row stride %d < %d", ldo, N);
@@ -1601,6 +1618,7 @@ static int gemm_tcgen05_impl(const void* x, const void* w, const float* bias, vo
         PTParams q;
         q.out = out;
         q.bias = bias;
+        q.act = g_launch_act;
         q.T = T;
         q.N = N;
         q.K = K;
@@ -1647,6 +1665,7 @@ static int gemm_tcgen05_impl(const void* x, const void* w, const float* bias, vo
         if (rc != FERRIS_OK) return rc;
     }
 
+    if (g_launch_act.kind) FERRIS_REFUSE("tensor-core gemm: only the kernels of long steps apply an activation (ask ferris_gemm_tcgen05_fuses_activation)");
     Params p;
     p.out = out;
     p.bias = bias;
@@ -1783,6 +1802,7 @@ FERRIS_API int ferris_qkv_rope_gemm_tcgen05(const void* x, const void* w, const 
     r.nkv = nkv;
     r.d = d;
     r.page_size = page_size;
+    g_launch_act = FerrisEpilogueAct{0, 0.0f, 0.0f};
     return run_tokens_m(x, w, bias, out, QKV_ROPE_BF16, T, N, K, ldx, ldw, ldo, rows_w, 0, &r, (cudaStream_t)stream);
 }
 

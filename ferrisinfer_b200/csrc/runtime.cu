@@ -28,6 +28,19 @@ bool ferris_pdl_enabled() {
 }
 FERRIS_API void ferris_set_pdl(int on) { g_pdl = on ? 1 : 0; }
 
+// The activation that the next bf16-storing product applies in its epilogue (see common.cuh).
+static FerrisEpilogueAct g_epilogue_act = {0, 0.0f, 0.0f};
+FERRIS_API void ferris_gemm_set_activation(int kind, float a, float b) {
+    g_epilogue_act.kind = kind;
+    g_epilogue_act.a = a;
+    g_epilogue_act.b = b;
+}
+FerrisEpilogueAct ferris_take_epilogue_act() {
+    const FerrisEpilogueAct e = g_epilogue_act;
+    g_epilogue_act.kind = 0;
+    return e;
+}
+
 // Compute capability of the current device as major * 10 + minor, or a negative cudaError_t.
 FERRIS_API int ferris_device_arch() {
     int dev = 0, major = 0, minor = 0;

@@ -523,6 +523,45 @@ def gemm(x, w, bias, out, accumulate: bool = False):
     gemm_simt(x, w, bias, out, accumulate)
 
 
+_EPILOGUE_ACTIVATIONS = {"xielu": 1, "silu": 2}
+_set_activation = None
+
+
+def gemm_activation(x, w, out, kind: str, coefficients=(0.0, 0.0), params: Optional[torch.Tensor] = None):
+    """out = a(x w^T): the plain feed-forward's up product with its activation.  bf16 on the weight-stationary kernel
+    (at most 16 tokens) or the tcgen05 kernels of long steps: the activation is applied to the fp32 accumulator in
+    the product's epilogue, before the one rounding to bf16
+    (``coefficients``: for xIELU, (softplus(p), 1/2 + softplus(q)) as Python floats).  Anything else: the product,
+    then the activation kernel with ``params`` (the two raw numbers on the device)."""
+    global _set_activation
+    if kind not in _EPILOGUE_ACTIVATIONS:
+        raise KernelError(f"activation '{kind}' is not known")
+    if out.dtype == torch.bfloat16 and w.dim() == 2 and w.shape[0] == out.shape[1]:
+        if _set_activation is None:
+            _set_activation = _lib().ferris_gemm_set_activation
+            _set_activation.argtypes = [_I, _F, _F]
+            _set_activation.restype = None
+        a, b = float(coefficients[0]), float(coefficients[1])
+        code = _EPILOGUE_ACTIVATIONS[kind]
+        try:  # the product that is launched next takes the activation; whatever happens, none is left behind
+            if x.shape[0] <= 16 and gemm_skinny_enabled() and _skinny_takes(x, w, out, 1):
+                _set_activation(code, a, b)
+                gemm_skinny(x, w, None, out, 0)
+                return
+            if isinstance(x, LazyRMSNorm):
+                x = x.materialize()
+            # of the tcgen05 kernels only those of long steps apply an activation
+            if tensor_core_gemm_takes(x, w) and _lib().ferris_gemm_tcgen05_fuses_activation(
+                    _c_int(x.shape[0]), _c_int(out.shape[1]), _c_int(x.shape[1]), _c_int(out.stride(0)), _ptr(out)):
+                _set_activation(code, a, b)
+                gemm_tcgen05(x, w, None, out, 0)
+                return
+        finally:
+            _set_activation(0, 0.0, 0.0)
+    gemm(x, w, None, out)
+    activation(out, out, kind, params)
+
+
 def gemm_swiglu(x, gate_up_weight, out, workspace=None):
     """out [T, I] = silu(x Wg^T) * (x Wu^T) with gate_up_weight = [Wg; Wu] ([2I, K]).  bf16: one tensor-core
     kernel with two accumulators (the [T, 2I] intermediate never exists); otherwise a product and the SwiGLU kernel."""

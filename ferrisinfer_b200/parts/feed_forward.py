@@ -48,7 +48,8 @@ class SwiGLU(FeedForward):
 class DenseActivation(FeedForward):
     """h += W_down a(W_up y), no gate, no bias.  ``activation``: "xielu" (two learned numbers p, q in the tensor
     ``act``: softplus(p) z^2 + z / 2 for z > 0, (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2 otherwise) or "silu".
-    The activation is evaluated in fp32 on the rounded product."""
+    The activation is evaluated in fp32: in the up product's epilogue on the accumulator where a tensor-core or
+    weight-stationary kernel runs the product (bf16), in a kernel of its own otherwise."""
 
     accepts_lazy_norm = True
     graph_safe = True
@@ -74,12 +75,16 @@ class DenseActivation(FeedForward):
         up, down, act = self._names
         self.up, self.down = tensors[f"{prefix}.{up}"], tensors[f"{prefix}.{down}"]
         self.act = tensors.get(f"{prefix}.{act}")
+        self.coefficients = (0.0, 0.0)
+        if self.act is not None:
+            # what the product's epilogue needs of the two learned numbers, formed once: softplus(p), 1/2 + softplus(q)
+            sp = torch.nn.functional.softplus(self.act.detach().to("cpu", torch.float32), threshold=20.0)
+            self.coefficients = (float(sp[0]), 0.5 + float(sp[1]))
 
     def forward(self, x, h, ctx):
         T, I = x.shape[0], self.intermediate_size
         z = ctx.workspace.get("ffn_act", (T, I), ctx.act_dtype)
-        ops.gemm(x, self.up, None, z)
-        ops.activation(z, z, self.activation, self.act)
+        ops.gemm_activation(x, self.up, z, self.activation, self.coefficients, self.act)
         ops.gemm(z, self.down, None, h, accumulate=True)
 
 

@@ -283,6 +283,31 @@ def test_xielu_activation(device, dtype, n):
     assert torch.isfinite(z).all()
 
 
+@pytest.mark.parametrize("T", [3, 16, 40, 130, 700])  # weight-stationary, tcgen05 short, token-major, CTA pairs
+@pytest.mark.parametrize("kind", ["xielu", "silu"])
+def test_up_product_with_the_activation_in_its_epilogue(device, T, kind):
+    ops = _ops()
+    torch.manual_seed(T)
+    K, N = 192, 520
+    x = torch.randn(T, K, device=device).to(BF16)
+    w = (torch.randn(N, K, device=device) / math.sqrt(K)).to(BF16)
+    params = torch.tensor([0.4, -1.1], device=device)
+    coefficients = (math.log1p(math.exp(0.4)), 0.5 + math.log1p(math.exp(-1.1)))
+    fused = torch.empty(T, N, dtype=BF16, device=device)
+    ops.gemm_activation(x, w, fused, kind, coefficients, params)
+    z = x.double() @ w.double().T
+    want = plain.xielu(z, 0.4, -1.1) if kind == "xielu" else plain.silu(z)
+    assert torch.allclose(fused.double(), want, atol=2e-2, rtol=2e-2)
+    # nothing is left behind for the next product
+    y = torch.empty(T, N, dtype=BF16, device=device)
+    ops.gemm(x, w, None, y)
+    assert torch.allclose(y.double(), z, atol=2e-2, rtol=2e-2)
+    # 32-bit: the product, then the activation kernel
+    out32 = torch.empty(T, N, device=device)
+    ops.gemm_activation(x.float(), w.float(), out32, kind, coefficients, params)
+    assert torch.allclose(out32.double(), want, atol=1e-4, rtol=1e-4)
+
+
 def paged(device, dtype, T, nkv, d, dv, page_size, order):
     """Empty caches and the block table of one request whose pages are ``order``."""
     pages = max(order) + 1
