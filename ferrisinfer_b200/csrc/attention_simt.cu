@@ -20,13 +20,45 @@ constexpr int ATT_THREADS = 128;
 constexpr int ATT_WARPS = ATT_THREADS / 32;
 constexpr int MAX_PER_LANE = 8;  // head size up to 256
 
+// What else enters a score and the softmax, per query head (any pointer may be null):
+//   slopes:        s_j += slopes[h] * (j - P), a penalty linear in the distance;
+//   log_r1, log_r2: s_j -= log_r1[h] * ln(1 + log_r2[h] * (P - j)), a penalty that grows with the distance's logarithm;
+//   sink:          the softmax's denominator also holds exp(sink[h]): a weight that belongs to no key and no value.
+// v_stride: elements between the value rows of consecutive cache rows (0: dv).  With the key cache given as the
+// value cache too and v_stride = d, a value is the first dv elements of its key (keys that carry their value).
+struct ScoreTerms {
+    const float* slopes;
+    const float* log_r1;
+    const float* log_r2;
+    const float* sink;
+    int v_stride;
+};
+struct HeadTerms {
+    int kind;  // 0: nothing, 1: slope, 2: logarithm
+    float a, b;
+};
+__device__ __forceinline__ HeadTerms head_terms(const ScoreTerms& st, int h) {
+    HeadTerms t = {0, 0.0f, 0.0f};
+    if (st.slopes) t.kind = 1, t.a = st.slopes[h];
+    if (st.log_r1) t.kind = 2, t.a = st.log_r1[h], t.b = st.log_r2[h];
+    return t;
+}
+// the score of the key at j for the query at P, from the scaled product
+__device__ __forceinline__ float with_terms(float s, const HeadTerms& t, int j, int P) {
+    if (t.kind == 1) return fmaf(t.a, (float)(j - P), s);
+    if (t.kind == 2) return s - t.a * log1pf(t.b * (float)(P - j));
+    return s;
+}
+// the sink's share of the denominator, relative to the maximum mm of the keys' scores
+__device__ __forceinline__ float sink_share(const ScoreTerms& st, int h, float mm) { return st.sink ? expf(st.sink[h] - mm) : 0.0f; }
+
 template <typename T>
 __global__ void __launch_bounds__(ATT_THREADS)
     paged_attention_simt_kernel(const T* q, int ldq, T* __restrict__ out, int ldo, const T* k_cache, const T* v_cache,
                                 const int* __restrict__ block_tables, int max_blocks,
                                 const int* __restrict__ token_seq, const int* __restrict__ positions, int nh,
                                 int nkv, int d, int dv, int page_size, int window, float scale,
-                                const float* __restrict__ slopes) {
+                                const ScoreTerms st) {
     extern __shared__ float smem[];  // per warp: m, z, acc[dv]
     pdl_wait();
     pdl_launch_dependents();
@@ -37,7 +69,8 @@ __global__ void __launch_bounds__(ATT_THREADS)
     const int P = positions[t];
     const int lo = (window > 0 && P - window + 1 > 0) ? P - window + 1 : 0;
     const int* table = block_tables + (size_t)seq * max_blocks;
-    const float slope = slopes ? slopes[hq] : 0.0f;
+    const HeadTerms ht = head_terms(st, hq);
+    const size_t vs = st.v_stride ? st.v_stride : dv;
 
     float qv[MAX_PER_LANE], acc[MAX_PER_LANE];
     const T* qrow = q + (size_t)t * ldq + (size_t)hq * d;
@@ -52,14 +85,14 @@ __global__ void __launch_bounds__(ATT_THREADS)
         const int page = table[j / page_size];
         if (page < 0) continue;  // a hole in the table: never reached for keys inside the window
         const size_t row = ((size_t)page * nkv + hk) * page_size + (j % page_size);
-        const size_t base = row * d, vbase = row * dv;
+        const size_t base = row * d, vbase = row * vs;
         float dot = 0.0f;
 #pragma unroll
         for (int r = 0; r < MAX_PER_LANE; ++r) {
             const int i = lane + 32 * r;
             if (i < d) dot = fmaf(qv[r], to_float(k_cache[base + i]), dot);
         }
-        const float s = slopes ? fmaf(slope, (float)(j - P), warp_sum(dot) * scale) : warp_sum(dot) * scale;
+        const float s = with_terms(warp_sum(dot) * scale, ht, j, P);
         float wgt;
         if (s > m) {
             const float rescale = expf(m - s);  // exp(-inf) = 0 on the first key
@@ -100,6 +133,7 @@ __global__ void __launch_bounds__(ATT_THREADS)
         f[w] = mw == -INFINITY ? 0.0f : expf(mw - mm);
         zz += smem[w * (dv + 2) + 1] * f[w];
     }
+    zz += sink_share(st, hq, mm);
     const float inv = 1.0f / zz;
     T* orow = out + (size_t)t * ldo + (size_t)hq * dv;
     for (int i = threadIdx.x; i < dv; i += ATT_THREADS) {
@@ -179,7 +213,7 @@ __global__ void __launch_bounds__(AL_THREADS)
                                  const int* __restrict__ block_tables, int max_blocks,
                                  const int* __restrict__ token_seq, const int* __restrict__ positions, int nh, int nkv,
                                  int d, int dv, int page_size, int window, float scale,
-                                 const float* __restrict__ slopes) {
+                                 const ScoreTerms st) {
     extern __shared__ float smem[];  // per group: m, z, acc[dv]
     pdl_wait();
     pdl_launch_dependents();
@@ -190,7 +224,8 @@ __global__ void __launch_bounds__(AL_THREADS)
     const int P = positions[t];
     const int lo = (window > 0 && P - window + 1 > 0) ? P - window + 1 : 0;
     const int* table = block_tables + (size_t)seq * max_blocks;
-    const float slope = slopes ? slopes[hq] : 0.0f;
+    const HeadTerms ht = head_terms(st, hq);
+    const size_t vs = st.v_stride ? st.v_stride : dv;
     const int ch = d >> 3, cv = dv >> 3;
     const int pshift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
 
@@ -217,7 +252,7 @@ __global__ void __launch_bounds__(AL_THREADS)
             for (int i = 0; i < MAXC; ++i) kk[u][i] = 0.0f, vv[u][i] = 0.0f;
             if (ok[u]) {
                 load_chunk<MAXC>(k_cache + row * d + sub * ch, ch, kk[u]);
-                load_chunk<MAXC>(v_cache + row * dv + sub * cv, cv, vv[u]);
+                load_chunk<MAXC>(v_cache + row * vs + sub * cv, cv, vv[u]);
             }
         }
         float dot[U];
@@ -235,7 +270,7 @@ __global__ void __launch_bounds__(AL_THREADS)
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             if (!ok[u]) continue;
-            const float s = slopes ? fmaf(slope, (float)(jj[u] - P), dot[u] * scale) : dot[u] * scale;
+            const float s = with_terms(dot[u] * scale, ht, jj[u], P);
             float wgt;
             if (s > m) {
                 const float rescale = expf(m - s);  // exp(-inf) = 0 on the first key
@@ -271,6 +306,7 @@ __global__ void __launch_bounds__(AL_THREADS)
         f[g] = mg == -INFINITY ? 0.0f : expf(mg - mm);
         zz += smem[g * (dv + 2) + 1] * f[g];
     }
+    zz += sink_share(st, hq, mm);
     const float inv = 1.0f / zz;
     T* orow = out + (size_t)t * ldo + (size_t)hq * dv;
     for (int i = threadIdx.x; i < dv; i += AL_THREADS) {
@@ -293,7 +329,7 @@ __global__ void __launch_bounds__(AG_THREADS)
                                   const int* __restrict__ block_tables, int max_blocks,
                                   const int* __restrict__ token_seq, const int* __restrict__ positions, int nh, int nkv,
                                   int d, int dv, int page_size, int window, float scale,
-                                  const float* __restrict__ slopes, int splits, float* __restrict__ partial) {
+                                  const ScoreTerms st, int splits, float* __restrict__ partial) {
     extern __shared__ float smem[];  // per group and head: m, z, acc[dv]
     pdl_wait();
     pdl_launch_dependents();
@@ -306,16 +342,18 @@ __global__ void __launch_bounds__(AG_THREADS)
     const int lo = (window > 0 && P - window + 1 > 0) ? P - window + 1 : 0;
     const int* table = block_tables + (size_t)seq * max_blocks;
     const int ch = d >> 4, cv = dv >> 4;
+    const size_t vs = st.v_stride ? st.v_stride : dv;
     const int pshift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
 
-    float qv[G][MAXC], acc[G][MAXC], m[G], z[G], slope[G];
+    float qv[G][MAXC], acc[G][MAXC], m[G], z[G];
+    HeadTerms ht[G];
 #pragma unroll
     for (int a = 0; a < G; ++a) {
 #pragma unroll
         for (int i = 0; i < MAXC; ++i) qv[a][i] = 0.0f, acc[a][i] = 0.0f;
         load_chunk<MAXC>(q + (size_t)t * ldq + (size_t)(h0 + a) * d + sub * ch, ch, qv[a]);
         m[a] = -INFINITY, z[a] = 0.0f;
-        slope[a] = slopes ? slopes[h0 + a] : 0.0f;
+        ht[a] = head_terms(st, h0 + a);
     }
     // the block's share of the keys lo .. P: with several splits, a run of `span` keys each
     const int span = (P - lo + splits) / splits;
@@ -339,7 +377,7 @@ __global__ void __launch_bounds__(AG_THREADS)
             for (int i = 0; i < MAXC; ++i) kk[u][i] = 0.0f, vv[u][i] = 0.0f;
             if (ok[u]) {
                 load_chunk<MAXC>(k_cache + row * d + sub * ch, ch, kk[u]);
-                load_chunk<MAXC>(v_cache + row * dv + sub * cv, cv, vv[u]);
+                load_chunk<MAXC>(v_cache + row * vs + sub * cv, cv, vv[u]);
             }
         }
         float dot[U][G];
@@ -363,7 +401,7 @@ __global__ void __launch_bounds__(AG_THREADS)
             if (!ok[u]) continue;
 #pragma unroll
             for (int a = 0; a < G; ++a) {
-                const float s = slopes ? fmaf(slope[a], (float)(jj[u] - P), dot[u][a] * scale) : dot[u][a] * scale;
+                const float s = with_terms(dot[u][a] * scale, ht[a], jj[u], P);
                 float wgt;
                 if (s > m[a]) {
                     const float rescale = expf(m[a] - s);
@@ -406,6 +444,7 @@ __global__ void __launch_bounds__(AG_THREADS)
             o += e[2 + i] * f;
         }
         if (splits == 1) {
+            zz += sink_share(st, h0 + a, mm);
             out[(size_t)t * ldo + (size_t)(h0 + a) * dv + i] = from_float<T>(o / zz);
         } else {  // the share's maximum, sum and weighted values, for the merge kernel
             float* e = partial + (((size_t)t * nh + h0 + a) * splits + split) * stride;
@@ -419,7 +458,7 @@ __global__ void __launch_bounds__(AG_THREADS)
 // ([tokens, heads, splits, 2 + dv]: maximum, sum, weighted values).  A block per (token, head).
 template <typename T>
 __global__ void __launch_bounds__(128) attention_merge_shares_kernel(const float* partial, T* __restrict__ out, int ldo,
-                                                                     int nh, int dv, int splits) {
+                                                                     int nh, int dv, int splits, const ScoreTerms st) {
     pdl_wait();
     pdl_launch_dependents();
     const int t = blockIdx.x, h = blockIdx.y;
@@ -432,6 +471,7 @@ __global__ void __launch_bounds__(128) attention_merge_shares_kernel(const float
         const float ms = base[(size_t)s2 * stride];
         zz += ms == -INFINITY ? 0.0f : base[(size_t)s2 * stride + 1] * expf(ms - mm);
     }
+    zz += sink_share(st, h, mm);
     const float inv = 1.0f / zz;
     for (int i = threadIdx.x; i < dv; i += blockDim.x) {
         float o = 0.0f;
@@ -446,7 +486,7 @@ __global__ void __launch_bounds__(128) attention_merge_shares_kernel(const float
 template <typename T, int G>
 void launch_shared(const void* q, int ldq, void* out, int ldo, const void* k_cache, const void* v_cache,
                    const int* block_tables, int max_blocks, const int* token_seq, const int* positions, int tokens, int nh,
-                   int nkv, int d, int dv, int page_size, int window, float scale, const float* slopes, int splits,
+                   int nkv, int d, int dv, int page_size, int window, float scale, const ScoreTerms st, int splits,
                    float* partial, cudaStream_t s) {
     const dim3 grid(tokens, nh / G, splits), block(AG_THREADS);
     const size_t smem = (size_t)AG_GROUPS * G * (dv + 2) * sizeof(float);
@@ -454,7 +494,7 @@ void launch_shared(const void* q, int ldq, void* out, int ldo, const void* k_cac
 #define FERRIS_AG_LAUNCH(MAXC, U)                                                                                       \
     ferris_launch(paged_attention_shared_kernel<T, MAXC, G, U>, grid, block, smem, s, (const T*)q, ldq, (T*)out, ldo,   \
                   (const T*)k_cache, (const T*)v_cache, block_tables, max_blocks, token_seq, positions, nh, nkv, d, dv,  \
-                  page_size, window, scale, slopes, splits, partial)
+                  page_size, window, scale, st, splits, partial)
     if (most <= 128)
         FERRIS_AG_LAUNCH(8, 4);
     else
@@ -462,20 +502,20 @@ void launch_shared(const void* q, int ldq, void* out, int ldo, const void* k_cac
 #undef FERRIS_AG_LAUNCH
     if (splits > 1)
         ferris_launch(attention_merge_shares_kernel<T>, dim3(tokens, nh), dim3(128), 0, s, (const float*)partial, (T*)out,
-                      ldo, nh, dv, splits);
+                      ldo, nh, dv, splits, st);
 }
 
 template <typename T>
 void launch_lanes(const void* q, int ldq, void* out, int ldo, const void* k_cache, const void* v_cache,
                   const int* block_tables, int max_blocks, const int* token_seq, const int* positions, int tokens, int nh,
-                  int nkv, int d, int dv, int page_size, int window, float scale, const float* slopes, cudaStream_t s) {
+                  int nkv, int d, int dv, int page_size, int window, float scale, const ScoreTerms st, cudaStream_t s) {
     const dim3 grid(tokens, nh), block(AL_THREADS);
     const size_t smem = (size_t)AL_GROUPS * (dv + 2) * sizeof(float);
     const int most = d > dv ? d : dv;
 #define FERRIS_AL_LAUNCH(MAXC, U)                                                                                      \
     ferris_launch(paged_attention_lanes_kernel<T, MAXC, U>, grid, block, smem, s, (const T*)q, ldq, (T*)out, ldo,      \
                   (const T*)k_cache, (const T*)v_cache, block_tables, max_blocks, token_seq, positions, nh, nkv, d, dv, \
-                  page_size, window, scale, slopes)
+                  page_size, window, scale, st)
     if (most <= 64)
         FERRIS_AL_LAUNCH(8, 2);
     else if (most <= 128)
@@ -522,7 +562,7 @@ __global__ void __launch_bounds__(TL_THREADS)
                                  const int* __restrict__ block_tables, int max_blocks,
                                  const int* __restrict__ token_seq, const int* __restrict__ positions, int tokens, int nh,
                                  int nkv, int d, int dv, int page_size, int window, float scale,
-                                 const float* __restrict__ slopes) {
+                                 const ScoreTerms st) {
     extern __shared__ __align__(16) float tl_smem[];
     const int dp = d + 4, dvp = dv + 4;
     float* Qs = tl_smem;                      // [64][d + 4], scaled
@@ -551,14 +591,14 @@ __global__ void __launch_bounds__(TL_THREADS)
     const int ry = tid >> 3, kx = tid & 7;
     const int r0 = 2 * ry;  // this lane's rows: r0 and r0 + 1
     int rt[2], rpos[2], rseq[2];
-    float rslope[2];
+    HeadTerms rterm[2];
 #pragma unroll
     for (int a = 0; a < 2; ++a) {
         rt[a] = t_first + (r0 + a) / g;
         const bool ok = rt[a] < t_end;
         rpos[a] = ok ? positions[rt[a]] : -1;
         rseq[a] = ok ? token_seq[rt[a]] : -1;
-        rslope[a] = slopes ? slopes[hk * g + (r0 + a) % g] : 0.0f;
+        rterm[a] = head_terms(st, hk * g + (r0 + a) % g);
     }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
     float acc[2][NC][4];
@@ -588,7 +628,7 @@ __global__ void __launch_bounds__(TL_THREADS)
                     const int in_page = pshift >= 0 ? (j & (page_size - 1)) : (j % page_size);
                     const size_t row = ((size_t)page * nkv + hk) * page_size + in_page;
                     stage_row(k_cache + row * d, Ks + key * dp, d, part, 8, 1.0f);
-                    stage_row(v_cache + row * dv, Vs + key * dvp, dv, part, 8, 1.0f);
+                    stage_row(v_cache + row * (st.v_stride ? (size_t)st.v_stride : (size_t)dv), Vs + key * dvp, dv, part, 8, 1.0f);
                 } else {
                     zero_row(Ks + key * dp, d, part, 8);
                     zero_row(Vs + key * dvp, dv, part, 8);
@@ -623,7 +663,7 @@ __global__ void __launch_bounds__(TL_THREADS)
                 for (int c = 0; c < 4; ++c) {
                     const int j = j0 + kx + 8 * c;
                     const bool seen = rseq[a] == sq && j >= lo && j <= rpos[a];
-                    sc[a][c] = seen ? fmaf(rslope[a], (float)(j - rpos[a]), sc[a][c]) : -INFINITY;
+                    sc[a][c] = seen ? with_terms(sc[a][c], rterm[a], j, rpos[a]) : -INFINITY;
                     best = fmaxf(best, sc[a][c]);
                 }
 #pragma unroll
@@ -670,7 +710,7 @@ __global__ void __launch_bounds__(TL_THREADS)
 #pragma unroll
     for (int a = 0; a < 2; ++a) {
         if (rt[a] >= t_end) continue;
-        const float inv = 1.0f / l[a];
+        const float inv = 1.0f / (l[a] + sink_share(st, hk * g + (r0 + a) % g, m[a]));
         T* orow = out + (size_t)rt[a] * ldo + (size_t)(hk * g + (r0 + a) % g) * dv;
 #pragma unroll
         for (int c = 0; c < NC; ++c) {
@@ -697,7 +737,7 @@ bool tiled_takes(int dtype, int nh, int nkv, int d, int dv) {
 template <typename T>
 int launch_tiled(const void* q, int ldq, void* out, int ldo, const void* k_cache, const void* v_cache,
                  const int* block_tables, int max_blocks, const int* token_seq, const int* positions, int tokens, int nh,
-                 int nkv, int d, int dv, int page_size, int window, float scale, const float* slopes, cudaStream_t s) {
+                 int nkv, int d, int dv, int page_size, int window, float scale, const ScoreTerms st, cudaStream_t s) {
     const int qt = TL_ROWS / (nh / nkv);
     const dim3 grid((tokens + qt - 1) / qt, nkv), block(TL_THREADS);
     const size_t smem = tiled_smem_bytes(d, dv);
@@ -707,7 +747,7 @@ int launch_tiled(const void* q, int ldq, void* out, int ldo, const void* k_cache
         if (e_ != FERRIS_OK) return e_;                                                                             \
         ferris_launch(paged_attention_tiled_kernel<T, NC>, grid, block, smem, s, (const T*)q, ldq, (T*)out, ldo,   \
                       (const T*)k_cache, (const T*)v_cache, block_tables, max_blocks, token_seq, positions, tokens, \
-                      nh, nkv, d, dv, page_size, window, scale, slopes);                                           \
+                      nh, nkv, d, dv, page_size, window, scale, st);                                           \
     } while (0)
     if (dv <= 64)
         FERRIS_TL_LAUNCH(2);
@@ -725,8 +765,13 @@ FERRIS_API int ferris_paged_attention_simt(const void* q, int ldq, void* out, in
                                            const void* v_cache, int dtype, const int* block_tables, int max_blocks,
                                            const int* token_seq, const int* positions, int tokens, int nh, int nkv,
                                            int d, int dv, int page_size, int window, float scale, const float* slopes,
+                                           const float* log_r1, const float* log_r2, const float* sink, int v_stride,
                                            int kv_span, float* scratch, long long scratch_floats, void* stream) {
     if (tokens <= 0) return FERRIS_OK;
+    if ((log_r1 == nullptr) != (log_r2 == nullptr)) FERRIS_REFUSE("attention: the logarithmic penalty needs both of its numbers per head");
+    if (slopes && log_r1) FERRIS_REFUSE("attention: a slope and a logarithmic penalty at once");
+    if (v_stride < 0 || (v_stride > 0 && v_stride < dv)) FERRIS_REFUSE("attention: value rows %d apart hold no %d values", v_stride, dv);
+    const ScoreTerms st = {slopes, log_r1, log_r2, sink, v_stride};
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0) FERRIS_REFUSE("attention: %d heads over %d kv heads", nh, nkv);
     if (d <= 0 || d > 32 * MAX_PER_LANE) FERRIS_REFUSE("attention: head size %d not in 1..%d", d, 32 * MAX_PER_LANE);
     if (dv <= 0 || dv > 32 * MAX_PER_LANE) FERRIS_REFUSE("attention: value head size %d not in 1..%d", dv, 32 * MAX_PER_LANE);
@@ -763,28 +808,28 @@ FERRIS_API int ferris_paged_attention_simt(const void* q, int ldq, void* out, in
         if (splits >= 1) {
             const int sp = (int)splits;
             if (dtype == FERRIS_F32) {
-                if (four) launch_shared<float, 4>(q, ldq, out, ldo, k_cache, v_cache, block_tables, max_blocks, token_seq, positions, tokens, nh, nkv, d, dv, page_size, window, scale, slopes, sp, scratch, s);
-                else launch_shared<float, 2>(q, ldq, out, ldo, k_cache, v_cache, block_tables, max_blocks, token_seq, positions, tokens, nh, nkv, d, dv, page_size, window, scale, slopes, sp, scratch, s);
+                if (four) launch_shared<float, 4>(q, ldq, out, ldo, k_cache, v_cache, block_tables, max_blocks, token_seq, positions, tokens, nh, nkv, d, dv, page_size, window, scale, st, sp, scratch, s);
+                else launch_shared<float, 2>(q, ldq, out, ldo, k_cache, v_cache, block_tables, max_blocks, token_seq, positions, tokens, nh, nkv, d, dv, page_size, window, scale, st, sp, scratch, s);
             } else {
-                if (four) launch_shared<bf16, 4>(q, ldq, out, ldo, k_cache, v_cache, block_tables, max_blocks, token_seq, positions, tokens, nh, nkv, d, dv, page_size, window, scale, slopes, sp, scratch, s);
-                else launch_shared<bf16, 2>(q, ldq, out, ldo, k_cache, v_cache, block_tables, max_blocks, token_seq, positions, tokens, nh, nkv, d, dv, page_size, window, scale, slopes, sp, scratch, s);
+                if (four) launch_shared<bf16, 4>(q, ldq, out, ldo, k_cache, v_cache, block_tables, max_blocks, token_seq, positions, tokens, nh, nkv, d, dv, page_size, window, scale, st, sp, scratch, s);
+                else launch_shared<bf16, 2>(q, ldq, out, ldo, k_cache, v_cache, block_tables, max_blocks, token_seq, positions, tokens, nh, nkv, d, dv, page_size, window, scale, st, sp, scratch, s);
             }
             FERRIS_LAUNCH_CHECK();
         }
     }
     if (d % 8 == 0 && dv % 8 == 0 && aligned && (size_t)AL_GROUPS * (dv + 2) * sizeof(float) <= 48 * 1024) {
         if (dtype == FERRIS_F32)
-            launch_lanes<float>(q, ldq, out, ldo, k_cache, v_cache, block_tables, max_blocks, token_seq, positions, tokens, nh, nkv, d, dv, page_size, window, scale, slopes, s);
+            launch_lanes<float>(q, ldq, out, ldo, k_cache, v_cache, block_tables, max_blocks, token_seq, positions, tokens, nh, nkv, d, dv, page_size, window, scale, st, s);
         else
-            launch_lanes<bf16>(q, ldq, out, ldo, k_cache, v_cache, block_tables, max_blocks, token_seq, positions, tokens, nh, nkv, d, dv, page_size, window, scale, slopes, s);
+            launch_lanes<bf16>(q, ldq, out, ldo, k_cache, v_cache, block_tables, max_blocks, token_seq, positions, tokens, nh, nkv, d, dv, page_size, window, scale, st, s);
         FERRIS_LAUNCH_CHECK();
     }
     if (dtype == FERRIS_F32)
         ferris_launch(paged_attention_simt_kernel<float>, grid, dim3(ATT_THREADS), smem, s, (const float*)q, ldq, (float*)out, ldo, (const float*)k_cache, (const float*)v_cache, block_tables,
-            max_blocks, token_seq, positions, nh, nkv, d, dv, page_size, window, scale, slopes);
+            max_blocks, token_seq, positions, nh, nkv, d, dv, page_size, window, scale, st);
     else if (dtype == FERRIS_BF16)
         ferris_launch(paged_attention_simt_kernel<bf16>, grid, dim3(ATT_THREADS), smem, s, (const bf16*)q, ldq, (bf16*)out, ldo, (const bf16*)k_cache, (const bf16*)v_cache, block_tables, max_blocks,
-            token_seq, positions, nh, nkv, d, dv, page_size, window, scale, slopes);
+            token_seq, positions, nh, nkv, d, dv, page_size, window, scale, st);
     else
         FERRIS_REFUSE("attention: unknown dtype %d", dtype);
     FERRIS_LAUNCH_CHECK();
@@ -801,8 +846,12 @@ FERRIS_API int ferris_paged_attention_tiled(const void* q, int ldq, void* out, i
                                             const void* v_cache, int dtype, const int* block_tables, int max_blocks,
                                             const int* token_seq, const int* positions, int tokens, int nh, int nkv,
                                             int d, int dv, int page_size, int window, float scale, const float* slopes,
+                                            const float* log_r1, const float* log_r2, const float* sink, int v_stride,
                                             void* stream) {
     if (tokens <= 0) return FERRIS_OK;
+    if ((log_r1 == nullptr) != (log_r2 == nullptr) || (slopes && log_r1)) FERRIS_REFUSE("tiled attention: one kind of distance penalty, with all its numbers");
+    if (v_stride < 0 || (v_stride > 0 && v_stride < dv)) FERRIS_REFUSE("tiled attention: value rows %d apart hold no %d values", v_stride, dv);
+    const ScoreTerms st = {slopes, log_r1, log_r2, sink, v_stride};
     if (dtype != FERRIS_F32 && dtype != FERRIS_BF16) FERRIS_REFUSE("attention: unknown dtype %d", dtype);
     if (page_size <= 0 || max_blocks <= 0) FERRIS_REFUSE("attention: page_size=%d max_blocks=%d", page_size, max_blocks);
     if (!tiled_takes(dtype, nh, nkv, d, dv)) FERRIS_REFUSE("tiled attention: %d heads over %d kv heads of %d / %d are not taken", nh, nkv, d, dv);
@@ -812,6 +861,6 @@ FERRIS_API int ferris_paged_attention_tiled(const void* q, int ldq, void* out, i
     if (nkv > 65535) FERRIS_REFUSE("attention: %d kv heads are more than one launch takes", nkv);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == FERRIS_F32)
-        return launch_tiled<float>(q, ldq, out, ldo, k_cache, v_cache, block_tables, max_blocks, token_seq, positions, tokens, nh, nkv, d, dv, page_size, window, scale, slopes, s);
-    return launch_tiled<bf16>(q, ldq, out, ldo, k_cache, v_cache, block_tables, max_blocks, token_seq, positions, tokens, nh, nkv, d, dv, page_size, window, scale, slopes, s);
+        return launch_tiled<float>(q, ldq, out, ldo, k_cache, v_cache, block_tables, max_blocks, token_seq, positions, tokens, nh, nkv, d, dv, page_size, window, scale, st, s);
+    return launch_tiled<bf16>(q, ldq, out, ldo, k_cache, v_cache, block_tables, max_blocks, token_seq, positions, tokens, nh, nkv, d, dv, page_size, window, scale, st, s);
 }

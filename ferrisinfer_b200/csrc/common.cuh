@@ -183,7 +183,7 @@ __device__ __forceinline__ void ferris_tl_value(int k, unsigned long long v) {
 // An activation in the epilogue of a matrix product that stores bf16 (the plain feed-forward's up product):
 // ferris_gemm_set_activation leaves it for the NEXT product launched through this library, which takes it (and clears
 // it) when it fills its parameters.  kind 0: none; 1: xIELU, a z^2 + z / 2 for z > 0 and b (exp(z) - 1 - z) + z / 2
-// otherwise; 2: SiLU.  Evaluated in fp32 on the accumulator, before the one rounding to bf16.
+// otherwise; 2: SiLU; 3: the square of max(z, 0).  Evaluated in fp32 on the accumulator, before the one rounding to bf16.
 // ---------------------------------------------------------------------------------------------
 struct FerrisEpilogueAct {
     int kind;
@@ -193,6 +193,7 @@ FerrisEpilogueAct ferris_take_epilogue_act();
 __device__ __forceinline__ float ferris_epilogue_act(float z, const FerrisEpilogueAct& e) {
     if (e.kind == 1) return z > 0.0f ? fmaf(e.a * z, z, 0.5f * z) : fmaf(e.b, expm1f(z) - z, 0.5f * z);
     if (e.kind == 2) return z / (1.0f + expf(-z));
+    if (e.kind == 3) return z > 0.0f ? z * z : 0.0f;
     return z;
 }
 

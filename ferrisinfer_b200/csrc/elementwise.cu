@@ -345,8 +345,11 @@ __global__ void embed_sinusoid_kernel(const T* __restrict__ table, const int* id
     if (!ok && threadIdx.x == 0 && status) atomicCAS(status, 0, t + 1);
     const T* row = table + (size_t)(ok ? id : 0) * hidden;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-        const float angle = pos * freq[i >> 1];
-        const float pe = (i & 1) ? cosf(angle) : sinf(angle);
+        float pe = 0.0f;  // no frequencies: no position vector, the scaled table row alone
+        if (freq) {
+            const float angle = pos * freq[i >> 1];
+            pe = (i & 1) ? cosf(angle) : sinf(angle);
+        }
         o[i] = ok ? fmaf(to_float(row[i]), scale, pe) : 0.0f;
     }
 }
@@ -484,7 +487,7 @@ FERRIS_API int ferris_add_f32(float* h, const float* x, long long n, void* strea
 // Activations of a plain (ungated) feed-forward, out[i] = a(in[i]), fp32 arithmetic.
 //   kind 0, xIELU with two learned numbers (p, q) in `params`:
 //     z > 0:  softplus(p) z^2 + z / 2;   z <= 0:  (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2
-//   kind 1, SiLU: z / (1 + exp(-z)).
+//   kind 1, SiLU: z / (1 + exp(-z)).   kind 2: the square of max(z, 0).
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.0f ? v : log1pf(expf(v)); }
 
@@ -503,6 +506,8 @@ __global__ void activation_kernel(const T* in, T* out, long long n, int kind,
         float r;
         if (kind == 0)
             r = z > 0.0f ? fmaf(a * z, z, 0.5f * z) : fmaf(b, expm1f(z) - z, 0.5f * z);
+        else if (kind == 2)
+            r = z > 0.0f ? z * z : 0.0f;
         else
             r = z / (1.0f + expf(-z));
         out[i] = from_float<T>(r);
@@ -512,6 +517,7 @@ __global__ void activation_kernel(const T* in, T* out, long long n, int kind,
 // The same, sixteen bytes a thread at a time (eight bf16 values or four floats), where the count and the addresses allow.
 __device__ __forceinline__ float activation_value(float z, int kind, float a, float b) {
     if (kind == 0) return z > 0.0f ? fmaf(a * z, z, 0.5f * z) : fmaf(b, expm1f(z) - z, 0.5f * z);
+    if (kind == 2) return z > 0.0f ? z * z : 0.0f;
     return z / (1.0f + expf(-z));
 }
 
@@ -546,7 +552,7 @@ __global__ void activation_vec_kernel(const uint4* in, uint4* out, long long n16
 FERRIS_API int ferris_activation(const void* in, void* out, int dtype, long long n, int kind, const float* params,
                                  void* stream) {
     if (n <= 0) return FERRIS_OK;
-    if (kind < 0 || kind > 1) FERRIS_REFUSE("activation: unknown kind %d", kind);
+    if (kind < 0 || kind > 2) FERRIS_REFUSE("activation: unknown kind %d", kind);
     if (kind == 0 && !params) FERRIS_REFUSE("activation: xIELU needs its two numbers");
     if (dtype != FERRIS_F32 && dtype != FERRIS_BF16) FERRIS_REFUSE("activation: unknown dtype %d", dtype);
     const int threads = 256;

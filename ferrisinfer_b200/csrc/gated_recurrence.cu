@@ -1,0 +1,297 @@
+// Recurrences over a state of fixed size whose decay changes from token to token, and what stands around them.
+//
+//   plain form (a state-space layer in its dual, attention-like reading):
+//       S_t = g_t S_(t-1) + k_t (b_t v_t)^T;              o_t = S_t^T q_t + D v_t
+//   delta rule (the state is corrected towards v_t along k_t before it is read):
+//       S' = g_t S_(t-1);  u = b_t (v_t - S'^T k_t);  S_t = S' + k_t u^T;   o_t = S_t^T q_t
+//
+// S: [dim, vdim] per (request, head), fp32, zero when the request is admitted; g_t (the decay) and b_t (a step size
+// or a gate) are one fp32 number per token and head, made by `recurrence_gates`; q and k come in `qk_heads` heads
+// shared by heads / qk_heads value heads each, and may carry one fp32 factor per (token, qk head) each (unit norms:
+// the factor is 1 / |x|, formed in fp32 by the gates kernel, so that the vectors themselves are read once as stored).
+//
+// The columns of S do not depend on one another.  A block owns 32 columns of one (request, head); four lanes share a
+// column, each holding rows sub, sub + 4, ... of it in registers.  Eight tokens' q, k (with their factors), the
+// block's 32 values, g and b stand in shared memory at a time; a token costs each lane 2-3 FMAs per held row and two
+// sums over the four lanes.  Tokens of a request are walked in order from its slot, so a step may hold single tokens,
+// portions of prompts or both.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int GR_THREADS = 128;
+constexpr int GR_LANES = 4;                      // lanes that share a column
+constexpr int GR_COLS = GR_THREADS / GR_LANES;   // columns of a block
+constexpr int GR_STAGE = 8;                      // tokens in shared memory at a time
+constexpr int GR_MAX_DIM = 256;
+
+__device__ __forceinline__ float softplus_g(float v) { return fmaxf(v, 0.0f) + log1pf(expf(-fabsf(v))); }
+
+// decay[t, h] = exp(-exp(A_log[h]) * dt), dt = softplus(a[t, h] + dt_bias[h]);  beta[t, h] = sigmoid(b[t, h]) (kind 0)
+// or dt itself (kind 1).  With unit norms: qscale[t, g] = q_mul / sqrt(sum q^2 + eps), kscale[t, g] = 1 / sqrt(sum k^2 + eps).
+template <typename T>
+__global__ void __launch_bounds__(128) recurrence_gates_kernel(const T* proj, int ld, int a_off, int b_off,
+                                                               const float* __restrict__ A_log,
+                                                               const float* __restrict__ dt_bias, float* __restrict__ decay,
+                                                               float* __restrict__ beta, int beta_kind, const T* qk, int ldqk,
+                                                               int q_off, int k_off, int qk_heads, int dim, float unit_eps,
+                                                               float q_mul, float* __restrict__ qscale,
+                                                               float* __restrict__ kscale, int heads) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    const T* row = proj + (size_t)t * ld;
+    for (int h = threadIdx.x; h < heads; h += blockDim.x) {
+        const float dt = softplus_g(to_float(row[a_off + h]) + dt_bias[h]);
+        decay[(size_t)t * heads + h] = expf(-expf(A_log[h]) * dt);
+        beta[(size_t)t * heads + h] = beta_kind == 0 ? 1.0f / (1.0f + expf(-to_float(row[b_off + h]))) : dt;
+    }
+    if (!qscale) return;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const T* src = qk + (size_t)t * ldqk;
+    for (int item = warp; item < 2 * qk_heads; item += warps) {
+        const bool is_q = item < qk_heads;
+        const int g = is_q ? item : item - qk_heads;
+        const T* x = src + (is_q ? q_off : k_off) + (size_t)g * dim;
+        float ss = 0.0f;
+        for (int i = lane; i < dim; i += 32) {
+            const float v = to_float(x[i]);
+            ss = fmaf(v, v, ss);
+        }
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss + unit_eps);
+        if (lane == 0) {
+            if (is_q)
+                qscale[(size_t)t * qk_heads + g] = inv * q_mul;
+            else
+                kscale[(size_t)t * qk_heads + g] = inv;
+        }
+    }
+}
+
+template <typename T, int KPL, bool DELTA>  // KPL rows of the state per lane: dim <= 4 * KPL
+__global__ void __launch_bounds__(GR_THREADS) gated_recurrence_kernel(
+    const T* q, int ldq, const T* k, int ldk, const T* v, int ldv, const float* decay, const float* beta,
+    const float* qscale, const float* kscale, const float* __restrict__ skip, float* __restrict__ out, int ldo,
+    float* state, const int* __restrict__ seq_q_start, const int* __restrict__ seq_state_slot, int heads, int qk_heads,
+    int dim, int vdim, int write_state) {
+    __shared__ float qs[GR_STAGE][4 * KPL];
+    __shared__ float ks[GR_STAGE][4 * KPL];
+    __shared__ float vs[GR_STAGE][GR_COLS];
+    __shared__ float gs[GR_STAGE], bs[GR_STAGE];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int seq = blockIdx.x, head = blockIdx.y;
+    const int tid = threadIdx.x, sub = tid & (GR_LANES - 1), cl = tid >> 2;
+    const int col = blockIdx.z * GR_COLS + cl;
+    const bool active = col < vdim;
+    const int qh = head / (heads / qk_heads);
+    const int row0 = seq_q_start[seq], row1 = seq_q_start[seq + 1];
+    if (row1 <= row0) return;
+    float* S = state + ((size_t)seq_state_slot[seq] * heads + head) * (size_t)dim * vdim;
+    float s[KPL];
+#pragma unroll
+    for (int i = 0; i < KPL; ++i) {
+        const int kk = sub + GR_LANES * i;
+        s[i] = (active && kk < dim) ? S[(size_t)kk * vdim + col] : 0.0f;
+    }
+    // rows of the staged vectors beyond the head's size stay zero
+    for (int i = tid; i < GR_STAGE * 4 * KPL; i += GR_THREADS) (&qs[0][0])[i] = 0.0f, (&ks[0][0])[i] = 0.0f;
+    const float d_skip = skip ? skip[head] : 0.0f;
+    for (int t0 = row0; t0 < row1; t0 += GR_STAGE) {
+        const int n = row1 - t0 < GR_STAGE ? row1 - t0 : GR_STAGE;
+        __syncthreads();  // the tokens before are done with (and the zeroing above has landed)
+        for (int i = tid; i < n * dim; i += GR_THREADS) {
+            const int r = i / dim, c = i - r * dim;
+            const size_t row = (size_t)(t0 + r);
+            const float fq = qscale ? qscale[row * qk_heads + qh] : 1.0f;
+            const float fk = kscale ? kscale[row * qk_heads + qh] : 1.0f;
+            qs[r][c] = to_float(q[row * ldq + (size_t)qh * dim + c]) * fq;
+            ks[r][c] = to_float(k[row * ldk + (size_t)qh * dim + c]) * fk;
+        }
+        for (int i = tid; i < n * GR_COLS; i += GR_THREADS) {
+            const int r = i / GR_COLS, c = i - r * GR_COLS;
+            const int cc = blockIdx.z * GR_COLS + c;
+            vs[r][c] = cc < vdim ? to_float(v[(size_t)(t0 + r) * ldv + (size_t)head * vdim + cc]) : 0.0f;
+        }
+        if (tid < n) {
+            gs[tid] = decay[(size_t)(t0 + tid) * heads + head];
+            bs[tid] = beta[(size_t)(t0 + tid) * heads + head];
+        }
+        __syncthreads();
+        for (int r = 0; r < n; ++r) {
+            const float g = gs[r], b = bs[r], vv = vs[r][cl];
+            float u, od = 0.0f;
+            if (DELTA) {
+                float dot = 0.0f;
+#pragma unroll
+                for (int i = 0; i < KPL; ++i) {
+                    s[i] *= g;
+                    dot = fmaf(s[i], ks[r][sub + GR_LANES * i], dot);
+                }
+                dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+                dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+                u = b * (vv - dot);
+#pragma unroll
+                for (int i = 0; i < KPL; ++i) {
+                    s[i] = fmaf(ks[r][sub + GR_LANES * i], u, s[i]);
+                    od = fmaf(s[i], qs[r][sub + GR_LANES * i], od);
+                }
+            } else {
+                u = b * vv;
+#pragma unroll
+                for (int i = 0; i < KPL; ++i) {
+                    s[i] = fmaf(g, s[i], ks[r][sub + GR_LANES * i] * u);
+                    od = fmaf(s[i], qs[r][sub + GR_LANES * i], od);
+                }
+            }
+            od += __shfl_xor_sync(0xffffffffu, od, 1);
+            od += __shfl_xor_sync(0xffffffffu, od, 2);
+            if (sub == 0 && active) out[(size_t)(t0 + r) * ldo + (size_t)head * vdim + col] = fmaf(d_skip, vv, od);
+        }
+    }
+    if (write_state && active) {
+#pragma unroll
+        for (int i = 0; i < KPL; ++i) {
+            const int kk = sub + GR_LANES * i;
+            if (kk < dim) S[(size_t)kk * vdim + col] = s[i];
+        }
+    }
+}
+
+// out = norm(o [* a(gate)]) * w [* a(gate)]: every `group` consecutive columns of a row divided by their own
+// sqrt(mean(.^2) + eps), times w[column % wlen]; the gate (a = sigmoid or SiLU) multiplies before the norm
+// (gate_first) or after it.  o fp32; gate and out in the activations' type.  A warp per group, a block per row.
+template <typename T>
+__global__ void __launch_bounds__(256) gated_group_norm_kernel(const float* o, int ldi, const T* gate, int ldg,
+                                                               const float* __restrict__ w, int wlen, T* __restrict__ out,
+                                                               int ldo, int n, int group, float eps, int gate_kind,
+                                                               int gate_first) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const float* orow = o + (size_t)t * ldi;
+    const T* grow = gate ? gate + (size_t)t * ldg : nullptr;
+    T* dst = out + (size_t)t * ldo;
+    for (int gi = warp; gi * group < n; gi += warps) {
+        const int base = gi * group;
+        float ss = 0.0f;
+        for (int i = lane; i < group; i += 32) {
+            float val = orow[base + i];
+            if (grow && gate_first) {
+                const float z = to_float(grow[base + i]);
+                const float sg = 1.0f / (1.0f + expf(-z));
+                val *= gate_kind == 1 ? z * sg : sg;
+            }
+            ss = fmaf(val, val, ss);
+        }
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)group + eps);
+        for (int i = lane; i < group; i += 32) {
+            float val = orow[base + i];
+            float gv = 1.0f;
+            if (grow) {
+                const float z = to_float(grow[base + i]);
+                const float sg = 1.0f / (1.0f + expf(-z));
+                gv = gate_kind == 1 ? z * sg : sg;
+            }
+            if (gate_first) val *= gv;
+            float y = (val * inv) * w[(base + i) % wlen];
+            if (!gate_first) y *= gv;
+            dst[base + i] = from_float<T>(y);
+        }
+    }
+}
+
+template <typename T, bool DELTA>
+int launch_recurrence(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv, const float* decay,
+                      const float* beta, const float* qscale, const float* kscale, const float* skip, float* out, int ldo,
+                      float* state, const int* seq_q_start, const int* seq_state_slot, int seqs, int heads, int qk_heads,
+                      int dim, int vdim, int write_state, cudaStream_t s) {
+    const dim3 grid(seqs, heads, (vdim + GR_COLS - 1) / GR_COLS), block(GR_THREADS);
+#define FERRIS_GR_LAUNCH(KPL)                                                                                          \
+    ferris_launch(gated_recurrence_kernel<T, KPL, DELTA>, grid, block, 0, s, (const T*)q, ldq, (const T*)k, ldk,      \
+                  (const T*)v, ldv, decay, beta, qscale, kscale, skip, out, ldo, state, seq_q_start, seq_state_slot,   \
+                  heads, qk_heads, dim, vdim, write_state)
+    if (dim <= 32)
+        FERRIS_GR_LAUNCH(8);
+    else if (dim <= 64)
+        FERRIS_GR_LAUNCH(16);
+    else if (dim <= 128)
+        FERRIS_GR_LAUNCH(32);
+    else
+        FERRIS_GR_LAUNCH(64);
+#undef FERRIS_GR_LAUNCH
+    FERRIS_LAUNCH_CHECK();
+}
+
+}  // namespace
+
+// proj: [tokens, ld] rows holding a (heads columns from a_off) and, for beta_kind 0, b (heads columns from b_off).
+// qk: rows holding q and k heads (qk_heads x dim each) from q_off / k_off; qscale / kscale (null: no unit norms):
+// fp32 [tokens, qk_heads].  decay, beta: fp32 [tokens, heads].
+FERRIS_API int ferris_recurrence_gates(const void* proj, int ld, int dtype, int a_off, int b_off, const float* A_log,
+                                       const float* dt_bias, float* decay, float* beta, int beta_kind, const void* qk,
+                                       int ldqk, int q_off, int k_off, int qk_heads, int dim, float unit_eps, float q_mul,
+                                       float* qscale, float* kscale, int tokens, int heads, void* stream) {
+    if (tokens <= 0) return FERRIS_OK;
+    if (heads <= 0 || !A_log || !dt_bias || !decay || !beta) FERRIS_REFUSE("recurrence gates: %d heads, or a table is missing", heads);
+    if (beta_kind != 0 && beta_kind != 1) FERRIS_REFUSE("recurrence gates: unknown kind %d of the second number", beta_kind);
+    if ((qscale == nullptr) != (kscale == nullptr)) FERRIS_REFUSE("recurrence gates: unit norms of q and k go together");
+    if (qscale && (!qk || qk_heads <= 0 || dim <= 0)) FERRIS_REFUSE("recurrence gates: unit norms of %d heads of %d", qk_heads, dim);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == FERRIS_F32)
+        ferris_launch(recurrence_gates_kernel<float>, dim3(tokens), dim3(128), 0, s, (const float*)proj, ld, a_off, b_off,
+                      A_log, dt_bias, decay, beta, beta_kind, (const float*)qk, ldqk, q_off, k_off, qk_heads, dim, unit_eps,
+                      q_mul, qscale, kscale, heads);
+    else if (dtype == FERRIS_BF16)
+        ferris_launch(recurrence_gates_kernel<bf16>, dim3(tokens), dim3(128), 0, s, (const bf16*)proj, ld, a_off, b_off,
+                      A_log, dt_bias, decay, beta, beta_kind, (const bf16*)qk, ldqk, q_off, k_off, qk_heads, dim, unit_eps,
+                      q_mul, qscale, kscale, heads);
+    else
+        FERRIS_REFUSE("recurrence gates: unknown dtype %d", dtype);
+    FERRIS_LAUNCH_CHECK();
+}
+
+// q, k: [tokens, qk_heads x dim] from their first column, rows ldq / ldk apart; v: [tokens, heads x vdim], rows ldv apart;
+// out: fp32 [tokens, heads x vdim]; state: fp32 [slots, heads, dim, vdim]; skip: fp32 [heads] or null.
+FERRIS_API int ferris_gated_recurrence(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv, int dtype,
+                                       const float* decay, const float* beta, const float* qscale, const float* kscale,
+                                       const float* skip, float* out, int ldo, float* state, const int* seq_q_start,
+                                       const int* seq_state_slot, int seqs, int heads, int qk_heads, int dim, int vdim,
+                                       int delta_rule, int write_state, void* stream) {
+    if (seqs <= 0) return FERRIS_OK;
+    if (heads <= 0 || qk_heads <= 0 || heads % qk_heads) FERRIS_REFUSE("recurrence: %d heads over %d q/k heads", heads, qk_heads);
+    if (dim <= 0 || dim > GR_MAX_DIM || vdim <= 0) FERRIS_REFUSE("recurrence: heads of %d x %d (at most %d rows)", dim, vdim, GR_MAX_DIM);
+    if (heads > 65535 || (vdim + GR_COLS - 1) / GR_COLS > 65535) FERRIS_REFUSE("recurrence: too many heads or columns for one launch");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == FERRIS_F32)
+        return delta_rule ? launch_recurrence<float, true>(q, ldq, k, ldk, v, ldv, decay, beta, qscale, kscale, skip, out, ldo, state, seq_q_start, seq_state_slot, seqs, heads, qk_heads, dim, vdim, write_state, s)
+                          : launch_recurrence<float, false>(q, ldq, k, ldk, v, ldv, decay, beta, qscale, kscale, skip, out, ldo, state, seq_q_start, seq_state_slot, seqs, heads, qk_heads, dim, vdim, write_state, s);
+    if (dtype == FERRIS_BF16)
+        return delta_rule ? launch_recurrence<bf16, true>(q, ldq, k, ldk, v, ldv, decay, beta, qscale, kscale, skip, out, ldo, state, seq_q_start, seq_state_slot, seqs, heads, qk_heads, dim, vdim, write_state, s)
+                          : launch_recurrence<bf16, false>(q, ldq, k, ldk, v, ldv, decay, beta, qscale, kscale, skip, out, ldo, state, seq_q_start, seq_state_slot, seqs, heads, qk_heads, dim, vdim, write_state, s);
+    FERRIS_REFUSE("recurrence: unknown dtype %d", dtype);
+}
+
+// o: fp32 [rows, n]; gate (may be null), out: the activations' type; w: fp32 [wlen], wlen dividing n.
+FERRIS_API int ferris_gated_group_norm(const float* o, int ldi, const void* gate, int ldg, const float* w, int wlen,
+                                       void* out, int ldo, int dtype, int rows, int n, int group, float eps,
+                                       int gate_kind, int gate_first, void* stream) {
+    if (rows <= 0) return FERRIS_OK;
+    if (n <= 0 || group <= 0 || n % group || wlen <= 0 || n % wlen) FERRIS_REFUSE("gated group norm: %d columns in groups of %d, %d weights", n, group, wlen);
+    if (gate_kind != 0 && gate_kind != 1) FERRIS_REFUSE("gated group norm: unknown gate %d", gate_kind);
+    const int groups = n / group;
+    const int threads = groups >= 8 ? 256 : (groups >= 4 ? 128 : (groups >= 2 ? 64 : 32));
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == FERRIS_F32)
+        ferris_launch(gated_group_norm_kernel<float>, dim3(rows), dim3(threads), 0, s, o, ldi, (const float*)gate, ldg, w, wlen, (float*)out, ldo, n, group, eps, gate_kind, gate_first);
+    else if (dtype == FERRIS_BF16)
+        ferris_launch(gated_group_norm_kernel<bf16>, dim3(rows), dim3(threads), 0, s, o, ldi, (const bf16*)gate, ldg, w, wlen, (bf16*)out, ldo, n, group, eps, gate_kind, gate_first);
+    else
+        FERRIS_REFUSE("gated group norm: unknown dtype %d", dtype);
+    FERRIS_LAUNCH_CHECK();
+}

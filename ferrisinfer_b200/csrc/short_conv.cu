@@ -1,5 +1,6 @@
-// A short causal convolution over time on each channel, added to its own input:
-//   u_t[c] = y_t[c] + sum_{j < taps} w[c, j] * y_(t - taps + 1 + j)[c],   y before the sequence's start = 0.
+// A short causal convolution over time on each channel:
+//   u_t[c] = a(r * y_t[c] + b[c] + sum_{j < taps} w[c, j] * y_(t - taps + 1 + j)[c]),   y before the sequence's start = 0,
+// with r = 1 (the convolution is added to its own input) or 0, an optional bias b and a = nothing or SiLU.
 // The taps - 1 inputs before a step's first token are the request's state ([slots, taps - 1, channels], fp32,
 // oldest first; zero when the request is admitted), so a sequence may be cut into steps anywhere.
 //
@@ -18,7 +19,7 @@ template <typename T>
 __global__ void __launch_bounds__(256) short_conv_apply_kernel(
     const T* y, int ldy, T* __restrict__ out, int ldo, const float* __restrict__ w, const float* state,
     const int* __restrict__ token_seq, const int* __restrict__ positions, const int* __restrict__ seq_start_pos,
-    const int* __restrict__ seq_state_slot, int channels, int taps) {
+    const int* __restrict__ seq_state_slot, int channels, int taps, const float* __restrict__ bias, int residual, int act) {
     pdl_wait();
     pdl_launch_dependents();
     const int t = blockIdx.x;
@@ -29,7 +30,7 @@ __global__ void __launch_bounds__(256) short_conv_apply_kernel(
     const int n = taps - 1;
     const float* st = state + (size_t)seq_state_slot[seq] * n * channels;
     const float own = to_float(y[(size_t)t * ldy + c]);
-    float acc = own;
+    float acc = (residual ? own : 0.0f) + (bias ? bias[c] : 0.0f);
     const float* wc = w + (size_t)c * taps;
     for (int j = 0; j < taps; ++j) {
         const int back = taps - 1 - j;
@@ -45,6 +46,7 @@ __global__ void __launch_bounds__(256) short_conv_apply_kernel(
             v = st[(size_t)(p - start + n) * channels + c];
         acc = fmaf(wc[j], v, acc);
     }
+    if (act) acc = acc / (1.0f + expf(-acc));
     out[(size_t)t * ldo + c] = from_float<T>(acc);
 }
 
@@ -73,7 +75,8 @@ __global__ void __launch_bounds__(256) short_conv_single_kernel(const T* y, int 
                                                                 const float* __restrict__ w, float* state,
                                                                 const int* __restrict__ positions,
                                                                 const int* __restrict__ seq_state_slot, int channels,
-                                                                int taps) {
+                                                                int taps, const float* __restrict__ bias, int residual,
+                                                                int act) {
     pdl_wait();
     pdl_launch_dependents();
     const int t = blockIdx.x;  // the request's only row of the step
@@ -84,7 +87,7 @@ __global__ void __launch_bounds__(256) short_conv_single_kernel(const T* y, int 
     float* st = state + (size_t)seq_state_slot[t] * n * channels + c;
     const float* wc = w + (size_t)c * taps;
     const float own = to_float(y[(size_t)t * ldy + c]);
-    float acc = own;
+    float acc = (residual ? own : 0.0f) + (bias ? bias[c] : 0.0f);
     for (int j = 0; j < n; ++j) {  // place j of the state is the input n - j positions back
         const float v = st[(size_t)j * channels];
         if (j > 0) st[(size_t)(j - 1) * channels] = v;
@@ -92,17 +95,20 @@ __global__ void __launch_bounds__(256) short_conv_single_kernel(const T* y, int 
     }
     acc = fmaf(wc[n], own, acc);
     if (n > 0) st[(size_t)(n - 1) * channels] = own;
+    if (act) acc = acc / (1.0f + expf(-acc));
     out[(size_t)t * ldo + c] = from_float<T>(acc);
 }
 
 }  // namespace
 
 // y, out: [tokens, channels] rows ldy / ldo apart (out must not be y); w: fp32 [channels, taps];
-// state: fp32 [slots, taps - 1, channels] (may be null when taps == 1).
+// state: fp32 [slots, taps - 1, channels] (may be null when taps == 1); bias: fp32 [channels] or null; residual: the
+// input is added to the convolution; act: 0 nothing, 1 SiLU of the sum.
 FERRIS_API int ferris_short_conv(const void* y, int ldy, void* out, int ldo, int dtype, const float* w, float* state,
                                  const int* token_seq, const int* positions, const int* seq_q_start,
                                  const int* seq_start_pos, const int* seq_state_slot, int tokens, int seqs, int channels,
-                                 int taps, int advance, int single_tokens, void* stream) {
+                                 int taps, int advance, int single_tokens, const float* bias, int residual, int act,
+                                 void* stream) {
     if (tokens <= 0 || seqs <= 0) return FERRIS_OK;
     if (channels <= 0 || taps <= 0) FERRIS_REFUSE("short conv: channels=%d taps=%d", channels, taps);
     if (taps > 1 && !state) FERRIS_REFUSE("short conv: %d taps need a state", taps);
@@ -114,23 +120,23 @@ FERRIS_API int ferris_short_conv(const void* y, int ldy, void* out, int ldo, int
     const dim3 block(threads), grid_a(tokens, tiles), grid_b(seqs, tiles);
     if (single_tokens && advance && tokens == seqs && dtype == FERRIS_F32) {
         ferris_launch(short_conv_single_kernel<float>, grid_a, block, 0, s, (const float*)y, ldy, (float*)out, ldo, w, state,
-                      positions, seq_state_slot, channels, taps);
+                      positions, seq_state_slot, channels, taps, bias, residual, act);
         FERRIS_LAUNCH_CHECK();
     }
     if (single_tokens && advance && tokens == seqs && dtype == FERRIS_BF16) {
         ferris_launch(short_conv_single_kernel<bf16>, grid_a, block, 0, s, (const bf16*)y, ldy, (bf16*)out, ldo, w, state,
-                      positions, seq_state_slot, channels, taps);
+                      positions, seq_state_slot, channels, taps, bias, residual, act);
         FERRIS_LAUNCH_CHECK();
     }
     if (dtype == FERRIS_F32) {
         ferris_launch(short_conv_apply_kernel<float>, grid_a, block, 0, s, (const float*)y, ldy, (float*)out, ldo, w,
-                      (const float*)state, token_seq, positions, seq_start_pos, seq_state_slot, channels, taps);
+                      (const float*)state, token_seq, positions, seq_start_pos, seq_state_slot, channels, taps, bias, residual, act);
         if (advance && taps > 1)
             ferris_launch(short_conv_advance_kernel<float>, grid_b, block, 0, s, (const float*)y, ldy, state, seq_q_start,
                           seq_state_slot, channels, taps);
     } else if (dtype == FERRIS_BF16) {
         ferris_launch(short_conv_apply_kernel<bf16>, grid_a, block, 0, s, (const bf16*)y, ldy, (bf16*)out, ldo, w,
-                      (const float*)state, token_seq, positions, seq_start_pos, seq_state_slot, channels, taps);
+                      (const float*)state, token_seq, positions, seq_start_pos, seq_state_slot, channels, taps, bias, residual, act);
         if (advance && taps > 1)
             ferris_launch(short_conv_advance_kernel<bf16>, grid_b, block, 0, s, (const bf16*)y, ldy, state, seq_q_start,
                           seq_state_slot, channels, taps);

@@ -523,7 +523,7 @@ def gemm(x, w, bias, out, accumulate: bool = False):
     gemm_simt(x, w, bias, out, accumulate)
 
 
-_EPILOGUE_ACTIVATIONS = {"xielu": 1, "silu": 2}
+_EPILOGUE_ACTIVATIONS = {"xielu": 1, "silu": 2, "relu2": 3}
 _set_activation = None
 
 
@@ -691,6 +691,21 @@ _attention_tiled = True
 ATTENTION_MAX_SHARES = 16  # most shares that the keys of a single token are cut into
 
 
+class ScoreTerms:
+    """What else enters an attention score and its softmax, per query head (fp32 [num_heads] tensors on the device, or
+    None): ``slopes`` (the score of the key at j for the query at P gets slopes[h] * (j - P) added), ``log_r1`` and
+    ``log_r2`` (it loses log_r1[h] * ln(1 + log_r2[h] * (P - j))), ``sink`` (the softmax's denominator also holds
+    exp(sink[h]): a weight with no key and no value)."""
+
+    __slots__ = ("slopes", "log_r1", "log_r2", "sink")
+
+    def __init__(self, slopes=None, log_r1=None, log_r2=None, sink=None):
+        self.slopes, self.log_r1, self.log_r2, self.sink = slopes, log_r1, log_r2, sink
+
+    def any(self) -> bool:
+        return any(t is not None for t in (self.slopes, self.log_r1, self.log_r2, self.sink))
+
+
 def set_attention_tiled(on: bool = True) -> None:
     """Portions of prompts on the general attention's tiled kernel (True, the default) or on the kernel of single
     tokens (False), for comparisons."""
@@ -701,11 +716,13 @@ def set_attention_tiled(on: bool = True) -> None:
 def paged_attention_simt(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                          block_tables: torch.Tensor, token_seq: torch.Tensor, positions: torch.Tensor,
                          num_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float,
-                         score_slopes: Optional[torch.Tensor] = None, v_head_dim: Optional[int] = None,
-                         max_q_len: int = 1, max_kv_len: int = 0, workspace=None):
+                         score_slopes=None, v_head_dim: Optional[int] = None,
+                         max_q_len: int = 1, max_kv_len: int = 0, workspace=None, values_in_keys: bool = False):
     """General attention over the paged cache; q is read from the first nh*d columns of ``qkv``.
     ``score_slopes`` (fp32 [num_heads]): the score of a query at position P and the key at position j gets
-    slopes[head] * (j - P) added.  ``v_head_dim``: size of a value head where it differs from the keys'.
+    slopes[head] * (j - P) added; or a ``ScoreTerms`` (slopes, a logarithmic distance penalty, a sink in the softmax's
+    denominator).  ``v_head_dim``: size of a value head where it differs from the keys'.  ``values_in_keys``: a key's
+    first ``v_head_dim`` elements are its value (``v_cache`` is then not read and may be None).
     ``max_q_len``: the most tokens a request brings; above one (portions of prompts) the kernel that shares tiles of
     keys among 64 query rows runs where it takes the geometry.  ``max_kv_len`` and ``workspace`` (a step of single
     tokens): the most keys a request holds, and where scratch comes from; the keys of a token are then cut into
@@ -714,10 +731,23 @@ def paged_attention_simt(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Te
     T, _, ldq = _rows(qkv, "attention queries")
     T2, width, ldo = _rows(out, "attention output")
     _need(k_cache, "key cache", qkv.dtype)
-    _need(v_cache, "value cache", qkv.dtype)
+    v_stride = 0
+    if values_in_keys:
+        if dv > head_dim:
+            raise KernelError(f"attention: keys of {head_dim} hold no values of {dv}")
+        v_cache, v_stride = k_cache[..., :dv], head_dim
+    else:
+        _need(v_cache, "value cache", qkv.dtype)
     _need(block_tables, "block tables", torch.int32)
     _need(token_seq, "token-to-request map", torch.int32)
     _need(positions, "positions", torch.int32)
+    terms = score_slopes if isinstance(score_slopes, ScoreTerms) else ScoreTerms(slopes=score_slopes)
+    score_slopes = terms.slopes
+    for name, t_ in (("logarithmic penalty", terms.log_r1), ("logarithmic penalty", terms.log_r2), ("sinks", terms.sink)):
+        if t_ is not None:
+            _need(t_, name, torch.float32)
+            if t_.numel() != num_heads:
+                raise KernelError(f"attention: one number of the {name} per query head is needed")
     if T != T2 or width != num_heads * dv or out.dtype != qkv.dtype or qkv.shape[1] < num_heads * head_dim:
         raise KernelError(f"attention: q {tuple(qkv.shape)}, out {tuple(out.shape)}")
     if (k_cache.dim() != 4 or k_cache.shape[1] != num_kv_heads or k_cache.shape[3] != head_dim or block_tables.dim() != 2
@@ -744,7 +774,8 @@ def paged_attention_simt(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Te
                                            _dt(qkv, "attention"), _ptr(block_tables), _c_int(block_tables.shape[1]),
                                            _ptr(token_seq), _ptr(positions), _c_int(T), _c_int(num_heads),
                                            _c_int(num_kv_heads), _c_int(head_dim), _c_int(dv), _c_int(k_cache.shape[2]),
-                                           _c_int(window or 0), _c_float(scale), _ptr(score_slopes), *extra, _stream()),
+                                           _c_int(window or 0), _c_float(scale), _ptr(score_slopes), _ptr(terms.log_r1),
+                                           _ptr(terms.log_r2), _ptr(terms.sink), _c_int(v_stride), *extra, _stream()),
         "paged attention", 2 if extra and extra[0].value > 0 else 1,
     )
 
@@ -755,12 +786,14 @@ def embed_sinusoid(table: torch.Tensor, ids: torch.Tensor, positions: torch.Tens
     _need(table, "embedding table")
     _need(ids, "token ids", torch.int32)
     _need(positions, "positions", torch.int32)
-    _need(freq, "position frequencies", torch.float32)
+    if freq is not None:  # None: no position vector, the scaled table row alone
+        _need(freq, "position frequencies", torch.float32)
     _need(out, "embedding output", torch.float32)
     T, H = out.shape
-    if table.dim() != 2 or table.shape[1] != H or ids.numel() != T or positions.numel() != T or freq.numel() != (H + 1) // 2:
+    if (table.dim() != 2 or table.shape[1] != H or ids.numel() != T or positions.numel() != T
+            or (freq is not None and freq.numel() != (H + 1) // 2)):
         raise KernelError(f"embed_sinusoid: table {tuple(table.shape)}, ids {tuple(ids.shape)}, out {tuple(out.shape)}, "
-                          f"{freq.numel()} frequencies")
+                          f"{0 if freq is None else freq.numel()} frequencies")
     _check(
         _lib().ferris_embed_sinusoid(_ptr(table), _c_int(_dt(table, "embedding table")), _ptr(ids), _ptr(positions),
                                      _ptr(freq), _c_float(scale), _ptr(out), _c_int(T), _c_int(H), _c_int(table.shape[0]),
@@ -824,13 +857,13 @@ def add_(h: torch.Tensor, x: torch.Tensor):
     _check(_lib().ferris_add_f32(_ptr(h), _ptr(x), ctypes.c_longlong(h.numel()), _stream()), "add")
 
 
-ACTIVATIONS = {"xielu": 0, "silu": 1}
+ACTIVATIONS = {"xielu": 0, "silu": 1, "relu2": 2}
 
 
 def activation(x: torch.Tensor, out: torch.Tensor, kind: str, params: Optional[torch.Tensor] = None):
     """out = a(x) element by element (``out`` may be ``x``).  ``xielu``: with softplus of the two numbers of
     ``params`` (fp32 [2]) as a = softplus(p), b = 1/2 + softplus(q): a z^2 + z / 2 for z > 0, b (exp(z) - 1 - z) + z / 2
-    otherwise.  ``silu``: z sigmoid(z)."""
+    otherwise.  ``silu``: z sigmoid(z).  ``relu2``: max(z, 0)^2."""
     _need(x, "activation input")
     _need(out, "activation output", x.dtype)
     if kind not in ACTIVATIONS or out.shape != x.shape:
@@ -877,8 +910,9 @@ def qk_prepare_cache_write(qkv: torch.Tensor, positions: torch.Tensor, slot_mapp
 
 
 def short_conv(y: torch.Tensor, out: torch.Tensor, weight: torch.Tensor, state: Optional[torch.Tensor], ctx,
-               advance: bool = True):
-    """out = y + causal convolution of y over time on each channel (``weight`` fp32 [channels, taps]), a request's
+               advance: bool = True, bias: Optional[torch.Tensor] = None, residual: bool = True, silu: bool = False):
+    """out = y + causal convolution of y over time on each channel (``weight`` fp32 [channels, taps]; without
+    ``residual`` the convolution alone; ``bias`` fp32 [channels] added; ``silu``: SiLU of the sum), a request's
     ``taps - 1`` inputs before the step taken from ``state`` (fp32 [slots, taps - 1, channels]) and, with
     ``advance``, the state moved on to the step's end.  ``ctx``: the step context (device arrays only)."""
     T, C, ldy = _rows(y, "convolution input")
@@ -887,6 +921,10 @@ def short_conv(y: torch.Tensor, out: torch.Tensor, weight: torch.Tensor, state: 
     taps = weight.shape[1]
     if (T2, C2) != (T, C) or out.dtype != y.dtype or weight.shape != (C, taps) or y.data_ptr() == out.data_ptr():
         raise KernelError(f"short conv: y {tuple(y.shape)}, out {tuple(out.shape)}, weight {tuple(weight.shape)}")
+    if bias is not None:
+        _need(bias, "convolution bias", torch.float32)
+        if bias.numel() != C:
+            raise KernelError(f"short conv: {bias.numel()} biases for {C} channels")
     if taps > 1:
         _need(state, "convolution state", torch.float32)
         if state.shape[1:] != (taps - 1, C):
@@ -898,7 +936,8 @@ def short_conv(y: torch.Tensor, out: torch.Tensor, weight: torch.Tensor, state: 
                                  _ptr(state if taps > 1 else None), _ptr(ctx.token_seq), _ptr(ctx.positions),
                                  _ptr(ctx.seq_q_start), _ptr(ctx.seq_start_pos), _ptr(ctx.seq_state_slot), _c_int(T),
                                  _c_int(ctx.num_seqs), _c_int(C), _c_int(taps), _c_int(1 if advance else 0),
-                                 _c_int(1 if single else 0), _stream()),
+                                 _c_int(1 if single else 0), _ptr(bias), _c_int(1 if residual else 0),
+                                 _c_int(1 if silu else 0), _stream()),
         "short conv", kernels,
     )
 
@@ -956,6 +995,257 @@ def gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps
         _lib().ferris_gated_rmsnorm(_ptr(o), _c_int(ldi), _ptr(gate), _c_int(ldg), _ptr(weight), _ptr(out), _c_int(ldo),
                                     _c_int(_dt(out, "gated norm")), _c_int(T), _c_int(n), _c_float(eps), _stream()),
         "gated rmsnorm",
+    )
+
+
+def recurrence_gates(proj: torch.Tensor, a_off: int, b_off: Optional[int], A_log: torch.Tensor, dt_bias: torch.Tensor,
+                     decay: torch.Tensor, beta: torch.Tensor, heads: int, unit_norm: Optional[tuple] = None):
+    """Per token and head: decay = exp(-exp(A_log) * dt) with dt = softplus(proj[:, a_off + h] + dt_bias); beta =
+    sigmoid(proj[:, b_off + h]), or dt itself where ``b_off`` is None.  ``unit_norm`` = (rows, q_off, k_off, qk_heads,
+    dim, eps, q_mul, qscale, kscale): the factors that make the q and k heads of ``rows`` unit vectors
+    (1 / sqrt(sum x^2 + eps); q's also times q_mul), fp32 [T, qk_heads] each.  All in fp32."""
+    T, width, ld = _rows(proj, "recurrence gates input")
+    _need(A_log, "A_log", torch.float32)
+    _need(dt_bias, "dt_bias", torch.float32)
+    _need(decay, "decays", torch.float32)
+    _need(beta, "step sizes", torch.float32)
+    if (A_log.numel() != heads or dt_bias.numel() != heads or decay.shape != (T, heads) or beta.shape != (T, heads)
+            or a_off + heads > width or (b_off is not None and b_off + heads > width)):
+        raise KernelError(f"recurrence gates: proj {tuple(proj.shape)}, {heads} heads, decay {tuple(decay.shape)}")
+    qk, ldqk, q_off, k_off, qk_heads, dim, eps, q_mul, qscale, kscale = None, 0, 0, 0, 0, 0, 0.0, 1.0, None, None
+    if unit_norm is not None:
+        qk, q_off, k_off, qk_heads, dim, eps, q_mul, qscale, kscale = unit_norm
+        T2, w2, ldqk = _rows(qk, "recurrence q and k")
+        _need(qscale, "q factors", torch.float32)
+        _need(kscale, "k factors", torch.float32)
+        if (T2 != T or qk.dtype != proj.dtype or max(q_off, k_off) + qk_heads * dim > w2 or qscale.shape != (T, qk_heads)
+                or kscale.shape != (T, qk_heads)):
+            raise KernelError(f"recurrence gates: q/k rows {tuple(qk.shape)} for {qk_heads} heads of {dim}")
+    _check(
+        _lib().ferris_recurrence_gates(_ptr(proj), _c_int(ld), _c_int(_dt(proj, "recurrence gates")), _c_int(a_off),
+                                       _c_int(-1 if b_off is None else b_off), _ptr(A_log), _ptr(dt_bias), _ptr(decay),
+                                       _ptr(beta), _c_int(1 if b_off is None else 0), _ptr(qk), _c_int(ldqk), _c_int(q_off),
+                                       _c_int(k_off), _c_int(qk_heads), _c_int(dim), _c_float(eps), _c_float(q_mul),
+                                       _ptr(qscale), _ptr(kscale), _c_int(T), _c_int(heads), _stream()),
+        "recurrence gates",
+    )
+
+
+def gated_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, beta: torch.Tensor,
+                     out: torch.Tensor, state: torch.Tensor, ctx, heads: int, qk_heads: int, dim: int, vdim: int,
+                     delta_rule: bool, qscale: Optional[torch.Tensor] = None, kscale: Optional[torch.Tensor] = None,
+                     skip: Optional[torch.Tensor] = None, write_state: bool = True):
+    """The recurrence of the step's tokens, request by request from each request's state (fp32 [slots, heads, dim, vdim]):
+    plain: S <- decay S + k (beta v)^T, o = S^T q + skip v;  delta rule: S <- decay S, u = beta (v - S^T k), S <- S + k u^T,
+    o = S^T q.  ``q``, ``k``: [T, qk_heads x dim] (views with contiguous rows; value head h uses q/k head
+    h / (heads / qk_heads)), optionally times one fp32 factor per (token, q/k head) each; ``v``: [T, heads x vdim];
+    ``decay``, ``beta``: fp32 [T, heads]; ``out``: fp32 [T, heads x vdim]."""
+    T, wq, ldq = _rows(q, "recurrence queries")
+    T1, wk, ldk = _rows(k, "recurrence keys")
+    T2, wv, ldv = _rows(v, "recurrence values")
+    T3, wo, ldo = _rows(out, "recurrence output")
+    _need(state, "recurrence state", torch.float32)
+    _need(decay, "decays", torch.float32)
+    _need(beta, "step sizes", torch.float32)
+    if (not (T == T1 == T2 == T3) or wq != qk_heads * dim or wk != qk_heads * dim or wv != heads * vdim or wo != heads * vdim
+            or out.dtype != torch.float32 or k.dtype != q.dtype or v.dtype != q.dtype or state.shape[1:] != (heads, dim, vdim)
+            or decay.shape != (T, heads) or beta.shape != (T, heads)):
+        raise KernelError(f"recurrence: q {tuple(q.shape)}, k {tuple(k.shape)}, v {tuple(v.shape)}, out {tuple(out.shape)}, "
+                          f"state {tuple(state.shape)}")
+    for name, t_ in (("q factors", qscale), ("k factors", kscale)):
+        if t_ is not None:
+            _need(t_, name, torch.float32)
+            if t_.shape != (T, qk_heads):
+                raise KernelError(f"recurrence: {name} {tuple(t_.shape)}")
+    if skip is not None:
+        _need(skip, "skip weights", torch.float32)
+        if skip.numel() != heads:
+            raise KernelError("recurrence: one skip weight per head is needed")
+    _check(
+        _lib().ferris_gated_recurrence(_ptr(q), _c_int(ldq), _ptr(k), _c_int(ldk), _ptr(v), _c_int(ldv),
+                                       _c_int(_dt(q, "recurrence")), _ptr(decay), _ptr(beta), _ptr(qscale), _ptr(kscale),
+                                       _ptr(skip), _ptr(out), _c_int(ldo), _ptr(state), _ptr(ctx.seq_q_start),
+                                       _ptr(ctx.seq_state_slot), _c_int(ctx.num_seqs), _c_int(heads), _c_int(qk_heads),
+                                       _c_int(dim), _c_int(vdim), _c_int(1 if delta_rule else 0),
+                                       _c_int(1 if write_state else 0), _stream()),
+        "gated recurrence",
+    )
+
+
+def gated_group_norm(o: torch.Tensor, gate: Optional[torch.Tensor], weight: torch.Tensor, eps: float, out: torch.Tensor,
+                     group: int, gate_kind: str = "sigmoid", gate_first: bool = False):
+    """out = norm(o [* a(gate)]) * weight [* a(gate)]: every ``group`` consecutive columns divided by their own
+    sqrt(mean(.^2) + eps); ``weight`` (fp32) repeats every ``weight.numel()`` columns; the gate (a = "sigmoid" or
+    "silu") multiplies before the norm (``gate_first``) or after it.  o fp32; gate and out in the activations' type."""
+    T, n, ldi = _rows(o, "gated norm input")
+    T3, n3, ldo = _rows(out, "gated norm output")
+    _need(weight, "gated norm weight", torch.float32)
+    ldg = 0
+    if gate is not None:
+        T2, n2, ldg = _rows(gate, "gate")
+        if (T2, n2) != (T, n) or gate.dtype != out.dtype:
+            raise KernelError(f"gated group norm: gate {tuple(gate.shape)} for {tuple(o.shape)}")
+    if o.dtype != torch.float32 or (T3, n3) != (T, n) or group <= 0 or n % group or n % weight.numel() \
+            or gate_kind not in ("sigmoid", "silu"):
+        raise KernelError(f"gated group norm: o {tuple(o.shape)}, out {tuple(out.shape)}, groups of {group}, "
+                          f"{weight.numel()} weights, gate '{gate_kind}'")
+    _check(
+        _lib().ferris_gated_group_norm(_ptr(o), _c_int(ldi), _ptr(gate), _c_int(ldg), _ptr(weight), _c_int(weight.numel()),
+                                       _ptr(out), _c_int(ldo), _c_int(_dt(out, "gated norm")), _c_int(T), _c_int(n),
+                                       _c_int(group), _c_float(eps), _c_int(1 if gate_kind == "silu" else 0),
+                                       _c_int(1 if gate_first else 0), _stream()),
+        "gated group norm",
+    )
+
+
+def streams_expand(h: torch.Tensor, xs: torch.Tensor, streams: int):
+    """xs [T, streams x W] = ``streams`` copies of every row of h [T, W]; both fp32."""
+    _need(h, "residual rows", torch.float32)
+    _need(xs, "residual streams", torch.float32)
+    T, W = h.shape
+    if xs.shape != (T, streams * W):
+        raise KernelError(f"streams: {tuple(h.shape)} into {tuple(xs.shape)} as {streams} streams")
+    _check(_lib().ferris_streams_expand(_ptr(h), _ptr(xs), _c_int(T), _c_int(streams), _c_int(W), _stream()), "streams expand")
+
+
+def streams_sum(xs: torch.Tensor, h: torch.Tensor, streams: int):
+    """h [T, W] = the sum of the ``streams`` rows of every token in xs [T, streams x W]; both fp32."""
+    _need(h, "residual rows", torch.float32)
+    _need(xs, "residual streams", torch.float32)
+    T, W = h.shape
+    if xs.shape != (T, streams * W):
+        raise KernelError(f"streams: {tuple(xs.shape)} into {tuple(h.shape)} as {streams} streams")
+    _check(_lib().ferris_streams_sum(_ptr(xs), _ptr(h), _c_int(T), _c_int(streams), _c_int(W), _stream()), "streams sum")
+
+
+def streams_step(xs: torch.Tensor, streams: int, write: Optional[tuple] = None, read: Optional[tuple] = None):
+    """One pass over every token's residual streams (xs fp32 [T, streams x W]): ``write`` = (y fp32 [T, W], mix fp32
+    [streams, streams] indexed [from, to], out fp32 [streams]): x_r <- sum_s mix[s, r] x_s + out[r] y, all r from the
+    old streams; then ``read`` = (in fp32 [streams], norm weight fp32 [W], eps, out [T, W] in the activations' type):
+    out = rmsnorm(sum_s in[s] x_s) * weight.  Either may be None."""
+    _need(xs, "residual streams", torch.float32)
+    T = xs.shape[0]
+    if xs.dim() != 2 or xs.shape[1] % streams:
+        raise KernelError(f"streams: {tuple(xs.shape)} as {streams} streams")
+    W = xs.shape[1] // streams
+    y = mix = out_w = in_w = norm_w = out = None
+    eps = 0.0
+    if write is not None:
+        y, mix, out_w = write
+        _need(y, "sublayer result", torch.float32)
+        _need(mix, "stream mixing matrix", torch.float32)
+        _need(out_w, "stream output weights", torch.float32)
+        if y.shape != (T, W) or mix.numel() != streams * streams or out_w.numel() != streams:
+            raise KernelError(f"streams write: y {tuple(y.shape)}, mix {tuple(mix.shape)}, out {tuple(out_w.shape)}")
+    if read is not None:
+        in_w, norm_w, eps, out = read
+        _need(in_w, "stream input weights", torch.float32)
+        _need(norm_w, "norm weight", torch.float32)
+        _need(out, "normed rows")
+        if in_w.numel() != streams or norm_w.numel() != W or out.shape != (T, W):
+            raise KernelError(f"streams read: in {tuple(in_w.shape)}, norm {tuple(norm_w.shape)}, out {tuple(out.shape)}")
+    _check(
+        _lib().ferris_streams_step(_ptr(xs), _ptr(y), _ptr(mix), _ptr(out_w), _ptr(in_w), _ptr(norm_w), _c_float(eps),
+                                   _ptr(out), _c_int(_dt(out, "normed rows") if out is not None else F32), _c_int(T),
+                                   _c_int(streams), _c_int(W), _stream()),
+        "streams step",
+    )
+
+
+def token_shift(x: torch.Tensor, out: torch.Tensor, shift: torch.Tensor, state: torch.Tensor, ctx, advance: bool = True):
+    """out_t = x_t + (x_(t-1) - x_t) * shift, x_(t-1) the unshifted row of the request's token before (zeros at position
+    0; across steps from ``state``, fp32 [slots, W], which ``advance`` moves on to the request's last row of this step)."""
+    _need(x, "token shift input")
+    _need(out, "token shift output", x.dtype)
+    _need(shift, "token shift weights", torch.float32)
+    _need(state, "token shift state", torch.float32)
+    T, W = x.shape
+    if out.shape != (T, W) or shift.numel() != W or state.dim() != 2 or state.shape[1] != W or x.data_ptr() == out.data_ptr():
+        raise KernelError(f"token shift: x {tuple(x.shape)}, out {tuple(out.shape)}, state {tuple(state.shape)}")
+    single = bool(advance and getattr(ctx, "max_q_len", 0) == 1 and T == ctx.num_seqs)
+    _check(
+        _lib().ferris_token_shift(_ptr(x), _ptr(out), _c_int(_dt(x, "token shift")), _ptr(shift), _ptr(state),
+                                  _ptr(ctx.token_seq), _ptr(ctx.positions), _ptr(ctx.seq_q_start), _ptr(ctx.seq_start_pos),
+                                  _ptr(ctx.seq_state_slot), _c_int(T), _c_int(ctx.num_seqs), _c_int(W),
+                                  _c_int(1 if advance else 0), _c_int(1 if single else 0), _stream()),
+        "token shift", 2 if (advance and not single) else 1,
+    )
+
+
+def branch_norm_sum(h: torch.Tensor, branches: list, coef: float, eps: float):
+    """h += coef * sum_b rmsnorm(y_b) * w_b over ``branches`` = [(y_b fp32 [T, W], w_b fp32 [W]), ...] (one to four)."""
+    _need(h, "residual rows", torch.float32)
+    n = len(branches)
+    ys = (ctypes.c_void_p * n)()
+    ws = (ctypes.c_void_p * n)()
+    for i, (y, w) in enumerate(branches):
+        _need(y, "branch result", torch.float32)
+        _need(w, "branch norm weight", torch.float32)
+        if y.shape != h.shape or w.numel() != h.shape[1]:
+            raise KernelError(f"branch norm: y {tuple(y.shape)}, w {tuple(w.shape)} for h {tuple(h.shape)}")
+        ys[i], ws[i] = y.data_ptr(), w.data_ptr()
+    _check(_lib().ferris_branch_norm_sum(ys, ws, _c_int(n), _c_float(coef), _c_float(eps), _ptr(h), _c_int(h.shape[0]),
+                                         _c_int(h.shape[1]), _stream()), "branch norm sum")
+
+
+def latent_prepare(proj: torch.Tensor, q_off: int, dkv_off: int, norm_weight: torch.Tensor, eps: float,
+                   positions: torch.Tensor, inv_freq: Optional[torch.Tensor], rot_dims: int,
+                   slot_mapping: Optional[torch.Tensor], cache: Optional[torch.Tensor], q_att: torch.Tensor, heads: int,
+                   dim: int, rot: int, rank: int, write_kv: bool = True):
+    """Between the input product and attention over a shared latent.  ``proj`` rows hold ``heads`` x [dim plain | rot
+    rotated] query dimensions from ``q_off`` and [rank latent | rot key] from ``dkv_off``.  The latent is RMS-normed
+    with ``norm_weight``, the key part and the heads' rotated query parts are rotated (rotate-half over the first
+    ``rot_dims``, angle = position * inv_freq[i]), [latent | key part] becomes the token's cache row (``cache``
+    [pages, 1, page size, rank + rot]) and the rotated query parts go to ``q_att`` [T, heads x (rank + rot)], behind
+    the first ``rank`` columns of each head (which the absorbed plain queries fill)."""
+    T, width, ld = _rows(proj, "latent input")
+    T2, wq, ldqa = _rows(q_att, "latent queries")
+    _need(positions, "positions", torch.int32)
+    if (T2 != T or q_att.dtype != proj.dtype or wq != heads * (rank + rot) or q_off + heads * (dim + rot) > width
+            or dkv_off + rank + rot > width or positions.numel() != T):
+        raise KernelError(f"latent prepare: proj {tuple(proj.shape)}, q_att {tuple(q_att.shape)}")
+    if rot_dims:
+        _need(inv_freq, "rotary frequencies", torch.float32)
+        if inv_freq.numel() != rot_dims // 2:
+            raise KernelError("latent prepare: one frequency per rotated pair is needed")
+    if write_kv:
+        _need(slot_mapping, "slot mapping", torch.int32)
+        _need(cache, "latent cache", proj.dtype)
+        _need(norm_weight, "latent norm weight", torch.float32)
+        if cache.dim() != 4 or cache.shape[1] != 1 or cache.shape[3] != rank + rot or norm_weight.numel() != rank:
+            raise KernelError(f"latent prepare: cache {tuple(cache.shape)} for rows of {rank} + {rot}")
+    _check(
+        _lib().ferris_latent_prepare(_ptr(proj), _c_int(ld), _c_int(_dt(proj, "latent prepare")), _c_int(q_off),
+                                     _c_int(dkv_off), _ptr(norm_weight), _c_float(eps), _ptr(positions), _ptr(inv_freq),
+                                     _c_int(rot_dims), _ptr(slot_mapping if write_kv else None),
+                                     _ptr(cache if write_kv else None), _ptr(q_att), _c_int(ldqa), _c_int(T), _c_int(heads),
+                                     _c_int(dim), _c_int(rot), _c_int(rank), _c_int(1 if write_kv else 0), _stream()),
+        "latent prepare",
+    )
+
+
+def head_gemm(x: torch.Tensor, x_head_stride: int, w: torch.Tensor, out: torch.Tensor, out_head_stride: int,
+              gate: Optional[torch.Tensor] = None):
+    """out[t, h * out_head_stride + n] = (sum_k x[t, h * x_head_stride + k] w[h, k, n]) * g, g = sigmoid(gate[t, h]) or 1.
+    ``w``: [heads, K, N] in the activations' type; fp32 sums."""
+    T, wx, ldx = _rows(x, "head product input")
+    T2, wo, ldo = _rows(out, "head product output")
+    _need(w, "head product weights", x.dtype)
+    if w.dim() != 3:
+        raise KernelError(f"head product: weights {tuple(w.shape)}")
+    H, K, N = w.shape
+    ldg = 0
+    if gate is not None:
+        T3, wg, ldg = _rows(gate, "head gates")
+        if T3 != T or wg != H or gate.dtype != x.dtype:
+            raise KernelError(f"head product: gates {tuple(gate.shape)} for {H} heads")
+    if T2 != T or out.dtype != x.dtype or (H - 1) * x_head_stride + K > wx or (H - 1) * out_head_stride + N > wo:
+        raise KernelError(f"head product: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    _check(
+        _lib().ferris_head_gemm(_ptr(x), _c_int(ldx), _c_int(x_head_stride), _ptr(w), _ptr(out), _c_int(ldo),
+                                _c_int(out_head_stride), _ptr(gate), _c_int(ldg), _c_int(_dt(x, "head product")), _c_int(T),
+                                _c_int(H), _c_int(K), _c_int(N), _stream()),
+        "head product",
     )
 
 
@@ -1109,20 +1399,23 @@ def attention_step(qkv, out, k_cache, v_cache, meta, ctx, num_heads, num_kv_head
 
 
 def paged_attention(qkv, out, k_cache, v_cache, block_tables, ctx, num_heads, num_kv_heads, head_dim, window, scale,
-                    score_slopes: Optional[torch.Tensor] = None, v_head_dim: Optional[int] = None):
+                    score_slopes=None, v_head_dim: Optional[int] = None, values_in_keys: bool = False):
     """Attention of the step's tokens over the paged cache (their own keys are in it already).
     ``ctx`` is the step context.  bf16 with head size 64 / 128 runs on the tensor cores: the split-KV
     kernel when every request brings one token, the prefill kernel otherwise; every other geometry, the
     32-bit path, scores with slopes added (``score_slopes``) and value heads of another size than the keys'
     (``v_head_dim``) run the general kernel."""
     _need(k_cache, "key cache", qkv.dtype)
-    _need(v_cache, "value cache", qkv.dtype)
-    _need(block_tables, "block tables", torch.int32)
-    if v_head_dim is not None and v_head_dim != head_dim:
+    if isinstance(score_slopes, ScoreTerms) and not score_slopes.any():
+        score_slopes = None
+    if values_in_keys or (v_head_dim is not None and v_head_dim != head_dim):
         paged_attention_simt(qkv, out, k_cache, v_cache, block_tables, ctx.token_seq, ctx.positions, num_heads,
                              num_kv_heads, head_dim, window, scale, score_slopes=score_slopes, v_head_dim=v_head_dim,
-                             max_q_len=ctx.max_q_len, max_kv_len=ctx.max_kv_len, workspace=ctx.workspace)
+                             max_q_len=ctx.max_q_len, max_kv_len=ctx.max_kv_len, workspace=ctx.workspace,
+                             values_in_keys=values_in_keys)
         return
+    _need(v_cache, "value cache", qkv.dtype)
+    _need(block_tables, "block tables", torch.int32)
     if k_cache.dim() != 4 or k_cache.shape[1] != num_kv_heads or k_cache.shape[3] != head_dim \
             or v_cache.shape != k_cache.shape or block_tables.dim() != 2:
         raise KernelError(f"attention: cache {tuple(k_cache.shape)}, tables {tuple(block_tables.shape)}")

@@ -1,6 +1,7 @@
 """Parts of a layer (mixer, feed-forward, norm, position encoding, block) and the model built from them."""
 
-from . import attention, block, embedding, feed_forward, linear_attention, norm, position, short_conv  # noqa: F401  (register the built-in kinds)
+from . import (attention, block, embedding, feed_forward, latent_attention, linear_attention, norm, position,  # noqa: F401
+               recurrent, residual_streams, short_conv, wrappers)  # (register the built-in kinds)
 from .base import (CombinedNeed, FeedForward, FixedState, LayerCache, Mixer, Norm, PagedKV, PagedMeta, Part, PositionEncoding,
                    SeqInfo, StepContext)
 from .model import DecoderModel, build_model

@@ -18,9 +18,13 @@ Options beyond the reference's layer, each a parameter of its own:
   ``v_head_dim``        value heads of another size than query and key heads
   ``qk_unit_norm_eps``  q and k heads divided by their own sqrt(mean(.^2) + eps), no weight
   ``query_temperature`` (coef, every): q at position p times 1 + coef * ln(floor((p + 1) / every) + 1)
-  ``tensor_names``      the folder's names of the four matrices under the prefix (then no biases are read)
-With any of the first three the step runs product -> norm / temperature / cache write -> attention -> product;
-the position encoding must then be one that rotates nothing (it may add slopes to the scores).
+  ``tensor_names``      the folder's names of the four matrices under the prefix (then no biases are read, unless
+                        ``bias_names`` names those of q, k and v)
+  ``sink_name``         a learned number per head under that name: the softmax's denominator also holds its
+                        exponential, a weight that belongs to no key and no value (unscaled, unbiased, counted once)
+With any of these but the names the step runs product -> norm / temperature / cache write -> attention -> product;
+the position encoding must then be one that rotates nothing (it may add slopes or a logarithmic distance penalty to
+the scores; one with learned numbers names them under the mixer's prefix).
 """
 
 from __future__ import annotations
@@ -46,7 +50,8 @@ class GroupedQueryAttention(Mixer):
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position: PartSpec, window: Optional[int] = None, scale: Optional[float] = None,
                  v_head_dim: Optional[int] = None, qk_unit_norm_eps: Optional[float] = None,
-                 query_temperature: Optional[tuple] = None, tensor_names: Optional[dict] = None):
+                 query_temperature: Optional[tuple] = None, tensor_names: Optional[dict] = None,
+                 bias_names: Optional[dict] = None, sink_name: Optional[str] = None):
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} heads cannot share {num_kv_heads} kv heads")
         self.hidden_size, self.num_heads = int(hidden_size), int(num_heads)
@@ -67,12 +72,15 @@ class GroupedQueryAttention(Mixer):
         self.v_size = self.num_kv_heads * self.v_head_dim
         self.o_size = self.num_heads * self.v_head_dim
         # the plain layer (the reference's) keeps its fused kernels; any option sends the step the general way
+        self.sink_name, self.sink = sink_name, None
         self.plain = (self.v_head_dim == self.head_dim and self.qk_unit_norm_eps is None
-                      and self.query_temperature is None)
+                      and self.query_temperature is None and sink_name is None
+                      and not getattr(self.position, "learned_scores", False))
         if not self.plain and getattr(self.position, "rotary_dim", 0):
             raise ValueError("unit-norm keys, a query temperature or value heads of their own size go with a "
                              "position encoding that rotates nothing")
         self.tensor_names = dict(tensor_names) if tensor_names else None
+        self.bias_names = dict(bias_names) if bias_names else None
         self.qkv_weight = self.qkv_bias = self.o_weight = None
 
     # ------------------------------------------------------------------ weights
@@ -88,18 +96,30 @@ class GroupedQueryAttention(Mixer):
             TensorSpec(self._matrix_name(prefix, "k"), (KV, H), "matrix"),
             TensorSpec(self._matrix_name(prefix, "v"), (self.v_size, H), "matrix"),
         ]
-        if not self.tensor_names:
+        if self.bias_names:
+            specs += [TensorSpec(f"{prefix}.{self.bias_names[n]}", (size,), "bias")
+                      for n, size in zip("qkv", (Q, KV, self.v_size))]
+        elif not self.tensor_names:
             specs += [
                 TensorSpec(f"{prefix}.q_proj.bias", (Q,), "bias", required=False),
                 TensorSpec(f"{prefix}.k_proj.bias", (KV,), "bias", required=False),
                 TensorSpec(f"{prefix}.v_proj.bias", (self.v_size,), "bias", required=False),
             ]
+        specs += self.position.tensor_specs(prefix)  # learned numbers of the position encoding, if it has any
+        if self.sink_name:
+            specs.append(TensorSpec(f"{prefix}.{self.sink_name}", (self.num_heads,), "vector"))
         return specs + [TensorSpec(self._matrix_name(prefix, "o"), (H, self.o_size), "matrix")]
 
     def bind(self, tensors, prefix):
         w = [tensors.pop(self._matrix_name(prefix, n)) for n in "qkv"]
         self.qkv_weight = torch.cat(w, dim=0).contiguous()
-        biases = [None if self.tensor_names else tensors.pop(f"{prefix}.{n}_proj.bias", None) for n in "qkv"]
+        if self.bias_names:
+            biases = [tensors.pop(f"{prefix}.{self.bias_names[n]}") for n in "qkv"]
+        else:
+            biases = [None if self.tensor_names else tensors.pop(f"{prefix}.{n}_proj.bias", None) for n in "qkv"]
+        self.position.bind(tensors, prefix)
+        if self.sink_name:
+            self.sink = tensors[f"{prefix}.{self.sink_name}"]
         if any(b is not None for b in biases):
             sizes = (self.q_size, self.kv_size, self.v_size)
             parts = [
@@ -128,8 +148,11 @@ class GroupedQueryAttention(Mixer):
             ops.qk_prepare_cache_write(qkv, ctx.positions, meta.slot_mapping, cache.k, cache.v, nh, nkv, d, dv,
                                        self.qk_unit_norm_eps, self.query_temperature, write_kv=owns_cache)
             out = ctx.workspace.get("attn_out", (T, self.o_size), x.dtype)
+            log = self.position.score_log_penalty(nh, qkv.device)
+            terms = ops.ScoreTerms(slopes=self.position.score_slopes(nh, qkv.device), sink=self.sink,
+                                   log_r1=None if log is None else log[0], log_r2=None if log is None else log[1])
             ops.paged_attention(qkv, out, cache.k, cache.v, meta.block_tables, ctx, nh, nkv, d, self.window or 0,
-                                self.scale, score_slopes=self.position.score_slopes(nh, qkv.device), v_head_dim=dv)
+                                self.scale, score_slopes=terms, v_head_dim=dv)
             ops.gemm(out, self.o_weight, None, h, accumulate=True)
             return
         table = self.position.rotary_table(qkv.device)

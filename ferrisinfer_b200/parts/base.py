@@ -26,7 +26,8 @@ class PagedKV:
     """The mixer keeps a key and a value of ``num_kv_heads x head_dim`` per token, in pages.
     ``window``: None = every past token is read; n = only the last n (the current one included),
     so pages that lie wholly behind the window are given back while the request runs.
-    ``v_head_dim``: size of a value head where it differs from a key head's (None = the same)."""
+    ``v_head_dim``: size of a value head where it differs from a key head's (None = the same; 0 = no value rows are
+    kept, for a mixer whose keys carry their values)."""
 
     num_kv_heads: int
     head_dim: int
@@ -196,6 +197,11 @@ class PositionEncoding(Part):
         """fp32 [num_heads] on ``device`` if the encoding adds ``slopes[head] * (j - P)`` to the score of the key at
         position j for the query at position P (a penalty linear in the distance; j <= P); None (the default) if it
         adds nothing to the scores.  Such scores are attended by the general kernel in every precision."""
+        return None
+
+    def score_log_penalty(self, num_heads: int, device=None) -> Optional[tuple]:
+        """(r1, r2), fp32 [num_heads] each on ``device``, if the score of the key at position j for the query at position
+        P loses r1[head] * ln(1 + r2[head] * (P - j)); None (the default) otherwise."""
         return None
 
 

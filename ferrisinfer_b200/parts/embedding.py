@@ -33,14 +33,15 @@ class TokenEmbedding(Part):
 class ScaledSinusoidalEmbedding(Part):
     """h[t, :] = E[id_t, :] * scale + pe(pos_t), with pe(p)[2i] = sin(p * base^(-2i / H)) and pe(p)[2i + 1] the cosine
     of the same angle.  The frequencies are formed in 64-bit on the host and rounded once; angles are fp32.
-    ``needs_positions``: the model hands ``forward`` the step's positions."""
+    ``needs_positions``: the model hands ``forward`` the step's positions.  ``base`` None: no position vector, the
+    scaled table row alone (registered as ``scaled_embedding``)."""
 
     needs_positions = True
 
     def __init__(self, vocab_size: int, hidden_size: int, scale: float = 1.0, base: float = 10000.0,
                  weight_name: str = "weight"):
         self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
-        self.scale, self.base, self.weight_name = float(scale), float(base), weight_name
+        self.scale, self.base, self.weight_name = float(scale), None if base is None else float(base), weight_name
         self.weight = None
         self._freq = {}
 
@@ -54,6 +55,8 @@ class ScaledSinusoidalEmbedding(Part):
         self.weight = tensors[self._name(prefix)]
 
     def frequencies(self, device) -> torch.Tensor:
+        if self.base is None:
+            return None
         key = str(device)
         if key not in self._freq:
             H = self.hidden_size
@@ -98,4 +101,7 @@ class OutputHead(Part):
 
 register_part("embedding", "token_embedding", TokenEmbedding)
 register_part("embedding", "scaled_sinusoidal_embedding", ScaledSinusoidalEmbedding)
+register_part("embedding", "scaled_embedding",
+              lambda vocab_size, hidden_size, scale=1.0, weight_name="weight": ScaledSinusoidalEmbedding(
+                  vocab_size, hidden_size, scale=scale, base=None, weight_name=weight_name))
 register_part("output", "linear_head", OutputHead)

@@ -47,7 +47,8 @@ class SwiGLU(FeedForward):
 
 class DenseActivation(FeedForward):
     """h += W_down a(W_up y), no gate, no bias.  ``activation``: "xielu" (two learned numbers p, q in the tensor
-    ``act``: softplus(p) z^2 + z / 2 for z > 0, (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2 otherwise) or "silu".
+    ``act``: softplus(p) z^2 + z / 2 for z > 0, (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2 otherwise), "silu" or
+    "relu2" (the square of max(z, 0)).
     The activation is evaluated in fp32: in the up product's epilogue on the accumulator where a tensor-core or
     weight-stationary kernel runs the product (bf16), in a kernel of its own otherwise."""
 

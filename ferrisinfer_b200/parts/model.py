@@ -93,11 +93,16 @@ class DecoderModel:
         probabilities fp32 [n]), each such row's best token and its probability instead of its logits."""
         T = ctx.num_tokens
         ctx.shared.clear()  # what parts share belongs to one pass; a context may be run again (to record a graph)
-        h = ctx.workspace.get("residual", (T, self.hidden_size), torch.float32)
+        S = self.plan.residual_streams
+        row = ctx.workspace.get("residual", (T, self.hidden_size), torch.float32)
         if getattr(self.embedding, "needs_positions", False):
-            self.embedding.forward(ctx.token_ids, h, ctx.positions)
+            self.embedding.forward(ctx.token_ids, row, ctx.positions)
         else:
-            self.embedding.forward(ctx.token_ids, h)
+            self.embedding.forward(ctx.token_ids, row)
+        h = row
+        if S > 1:  # several residual streams a token: the blocks work on [T, S x H], the sum comes back into ``row``
+            h = ctx.workspace.get("residual_streams", (T, S * self.hidden_size), torch.float32)
+            ops.streams_expand(row, h, S)
         embedded = None
         if any(step.add_embedding for step in self.plan.run_order):
             embedded = ctx.workspace.get("embedding_output", (T, self.hidden_size), torch.float32)
@@ -108,9 +113,14 @@ class DecoderModel:
                 ops.add_(h, embedded)
             self.blocks[step.layer].forward(h, ctx, caches[owner], owns_cache=step.cache_of is None)
             if self.after_run is not None:
-                self.after_run(i, h)
+                if S > 1:
+                    ops.streams_sum(h, row, S)
+                self.after_run(i, row)
         if logits_index is None or logits_index.numel() == 0:
             return None
+        if S > 1:
+            ops.streams_sum(h, row, S)
+            h = row
         n = logits_index.numel()
         y = ctx.workspace.get("final_normed", (n, self.hidden_size), ctx.act_dtype)
         self.final_norm.forward(h, y, row_index=logits_index)

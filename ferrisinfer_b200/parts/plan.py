@@ -88,8 +88,15 @@ class ModelPlan:
     output_prefix: str
     max_positions: int
     extra: dict = field(default_factory=dict)
+    # residual rows per token: above one, the blocks get [T, streams x hidden] rows that all start as the embedding
+    # output, and the final norm reads their sum (block kinds made for it, such as ``residual_streams``)
+    residual_streams: int = 1
 
     def validate(self) -> None:
+        if self.residual_streams < 1:
+            raise ValueError(f"{self.residual_streams} residual streams")
+        if self.residual_streams > 1 and any(step.add_embedding for step in self.run_order):
+            raise ValueError("adding the embedding output again is not defined over several residual streams")
         for i, step in enumerate(self.run_order):
             if not (0 <= step.layer < len(self.layers)):
                 raise ValueError(f"run_order[{i}] names layer {step.layer}, which does not exist")

@@ -20,7 +20,7 @@ import numpy as np
 import torch
 
 from ..kernels import ops
-from .base import PositionEncoding
+from .base import PositionEncoding, TensorSpec
 from .plan import register_part
 
 
@@ -93,6 +93,35 @@ class DistanceSlopes(PositionEncoding):
         return self._device[key]
 
 
+class LogDistancePenalty(PositionEncoding):
+    """Nothing is rotated; the score of the key at position j for the query at position P loses
+    r1_h * ln(1 + r2_h * (P - j)), with two learned numbers per head, named ``r1_name`` and ``r2_name`` under the
+    mixer's prefix."""
+
+    graph_safe = True
+    learned_scores = True  # its numbers come from the folder: the mixer asks for its tensors and attends the general way
+
+    def __init__(self, num_heads: int, r1_name: str = "r1", r2_name: str = "r2"):
+        self.num_heads, self.r1_name, self.r2_name = int(num_heads), r1_name, r2_name
+        self.r1 = self.r2 = None
+
+    def rotary_table(self, device=None):
+        return None, 0
+
+    def tensor_specs(self, prefix):
+        return [TensorSpec(f"{prefix}.{self.r1_name}", (self.num_heads,), "vector"),
+                TensorSpec(f"{prefix}.{self.r2_name}", (self.num_heads,), "vector")]
+
+    def bind(self, tensors, prefix):
+        self.r1, self.r2 = tensors[f"{prefix}.{self.r1_name}"], tensors[f"{prefix}.{self.r2_name}"]
+
+    def score_log_penalty(self, num_heads, device=None):
+        if num_heads != self.num_heads:
+            raise ValueError(f"a distance penalty for {self.num_heads} heads, asked for {num_heads}")
+        return self.r1, self.r2
+
+
 register_part("position", "rotary", RotaryEncoding)
+register_part("position", "log_distance_penalty", LogDistancePenalty)
 register_part("position", "distance_slopes", DistanceSlopes)
 register_part("position", "none", NoPosition)

@@ -1,0 +1,176 @@
+"""Mixers that keep a state of fixed size per request and a decay that changes from token to token.
+
+``GatedDeltaRule``:
+  q, k (qk_heads x dim) and v (heads x vdim) = SiLU(conv(y W^T)), a short causal convolution per channel; q and k are
+  made unit vectors per head (1 / sqrt(sum x^2 + 1e-6)), q also times dim^(-1/2); per value head (which reads q/k head
+  h / (heads / qk_heads)): beta = sigmoid(y Wb^T), g = exp(-exp(A_log) softplus(y Wa^T + dt_bias));
+    S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q          (the read-out sees the token's own write)
+  h += (rmsnorm_per_head(o) * n * SiLU(y Wg^T)) Wo^T,   n of size vdim, shared by the heads.
+
+``StateSpaceDuality`` (a selective state-space layer in its attention-like reading):
+  y W_in^T = [z: inner | x: inner | B: groups x N | C: groups x N | dt: heads], inner = heads x vdim;
+  x, B, C = SiLU(conv(.) + bias);  dt = softplus(dt + dt_bias);  per head (group h / (heads / groups)):
+    S <- exp(-exp(A_log) dt) S + dt B x^T;  o = S^T C + D x
+  h += (rmsnorm_in_groups(o * SiLU(z)) * n) Wo^T       the gate before the norm, ``norm_groups`` equal parts.
+
+Both hold all input matrices as one, so that one product feeds the convolution, the gates and the recurrence; the
+state ([heads, dim, vdim] fp32) and the convolution's last taps - 1 inputs are carried in the request's slot, so a
+sequence may be cut anywhere.  Decays, step sizes, unit norms, the recurrence and the norms are fp32 whatever the
+activations' type.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from .base import CombinedNeed, FixedState, LayerCache, Mixer, TensorSpec
+from .plan import register_part
+
+
+def _fused_rows(parts: list) -> torch.Tensor:
+    """The matrices one below the other, with zero rows added up to a multiple of eight (rows of the product's
+    output then start on 16 bytes in either type)."""
+    w = torch.cat(parts, dim=0)
+    pad = (-w.shape[0]) % 8
+    if pad:
+        w = torch.cat([w, torch.zeros(pad, w.shape[1], dtype=w.dtype, device=w.device)], dim=0)
+    return w.contiguous()
+
+
+class GatedDeltaRule(Mixer):
+    accepts_lazy_norm = True
+    graph_safe = True
+
+    def __init__(self, hidden_size: int, num_heads: int, num_qk_heads: int, head_dim: int, v_head_dim: int,
+                 conv_taps: int, norm_eps: float, unit_norm_eps: float = 1e-6):
+        if num_heads % num_qk_heads:
+            raise ValueError(f"{num_heads} heads cannot share {num_qk_heads} q/k heads")
+        if head_dim > 256:
+            raise ValueError(f"heads of {head_dim} are larger than the recurrence kernel takes (256)")
+        self.hidden_size, self.num_heads, self.num_qk_heads = int(hidden_size), int(num_heads), int(num_qk_heads)
+        self.head_dim, self.v_head_dim, self.taps = int(head_dim), int(v_head_dim), int(conv_taps)
+        self.norm_eps, self.unit_norm_eps = float(norm_eps), float(unit_norm_eps)
+        self.qk_size = self.num_qk_heads * self.head_dim
+        self.v_size = self.num_heads * self.v_head_dim
+        self.conv_size = 2 * self.qk_size + self.v_size
+
+    def tensor_specs(self, prefix):
+        H, nh = self.hidden_size, self.num_heads
+        return [
+            TensorSpec(f"{prefix}.q", (self.qk_size, H), "matrix"),
+            TensorSpec(f"{prefix}.q.conv", (self.qk_size, self.taps), "vector"),
+            TensorSpec(f"{prefix}.k", (self.qk_size, H), "matrix"),
+            TensorSpec(f"{prefix}.k.conv", (self.qk_size, self.taps), "vector"),
+            TensorSpec(f"{prefix}.v", (self.v_size, H), "matrix"),
+            TensorSpec(f"{prefix}.v.conv", (self.v_size, self.taps), "vector"),
+            TensorSpec(f"{prefix}.b", (nh, H), "matrix"),
+            TensorSpec(f"{prefix}.A_log", (nh,), "vector"),
+            TensorSpec(f"{prefix}.norm", (self.v_head_dim,), "norm"),
+            TensorSpec(f"{prefix}.a", (nh, H), "matrix"),
+            TensorSpec(f"{prefix}.dt_bias", (nh,), "vector"),
+            TensorSpec(f"{prefix}.g", (self.v_size, H), "matrix"),
+            TensorSpec(f"{prefix}.o", (H, self.v_size), "matrix"),
+        ]
+
+    def bind(self, tensors, prefix):
+        # one product: [q | k | v | gate | b | a]
+        self.in_weight = _fused_rows([tensors.pop(f"{prefix}.{n}") for n in ("q", "k", "v", "g", "b", "a")])
+        self.conv_weight = torch.cat([tensors.pop(f"{prefix}.{n}.conv") for n in "qkv"], dim=0).contiguous()
+        self.A_log, self.dt_bias = tensors[f"{prefix}.A_log"], tensors[f"{prefix}.dt_bias"]
+        self.norm_weight, self.o_weight = tensors[f"{prefix}.norm"], tensors[f"{prefix}.o"]
+
+    def cache_need(self):
+        history = FixedState((self.taps - 1, self.conv_size), torch.float32) if self.taps > 1 else None
+        return CombinedNeed((history, FixedState((self.num_heads, self.head_dim, self.v_head_dim), torch.float32)))
+
+    def forward(self, x, h, ctx, cache: LayerCache, owns_cache: bool):
+        T = x.shape[0]
+        nh, g, d, dv = self.num_heads, self.num_qk_heads, self.head_dim, self.v_head_dim
+        QK, V, C = self.qk_size, self.v_size, self.conv_size
+        history, state = cache.parts
+        ws = ctx.workspace
+        proj = ws.get("recurrent_in", (T, self.in_weight.shape[0]), ctx.act_dtype)
+        ops.gemm(x, self.in_weight, None, proj)
+        conv = ws.get("recurrent_conv", (T, C), ctx.act_dtype)
+        ops.short_conv(proj[:, :C], conv, self.conv_weight, None if history is None else history.state, ctx,
+                       advance=owns_cache, residual=False, silu=True)
+        decay, beta = ws.get("recurrent_decay", (T, nh), torch.float32), ws.get("recurrent_beta", (T, nh), torch.float32)
+        qscale, kscale = ws.get("recurrent_qscale", (T, g), torch.float32), ws.get("recurrent_kscale", (T, g), torch.float32)
+        ops.recurrence_gates(proj, C + V + nh, C + V, self.A_log, self.dt_bias, decay, beta, nh,
+                             unit_norm=(conv, 0, QK, g, d, self.unit_norm_eps, d ** -0.5, qscale, kscale))
+        o = ws.get("recurrent_out", (T, V), torch.float32)
+        ops.gated_recurrence(conv[:, :QK], conv[:, QK:2 * QK], conv[:, 2 * QK:], decay, beta, o, state.state, ctx, nh, g, d, dv,
+                             delta_rule=True, qscale=qscale, kscale=kscale, write_state=owns_cache)
+        y = ws.get("recurrent_gated", (T, V), ctx.act_dtype)
+        ops.gated_group_norm(o, proj[:, C:C + V], self.norm_weight, self.norm_eps, y, group=dv, gate_kind="silu")
+        ops.gemm(y, self.o_weight, None, h, accumulate=True)
+
+
+class StateSpaceDuality(Mixer):
+    accepts_lazy_norm = True
+    graph_safe = True
+
+    def __init__(self, hidden_size: int, num_heads: int, v_head_dim: int, state_size: int, groups: int, norm_groups: int,
+                 conv_taps: int, norm_eps: float):
+        if num_heads % groups:
+            raise ValueError(f"{num_heads} heads cannot share {groups} groups")
+        if (num_heads * v_head_dim) % norm_groups:
+            raise ValueError(f"{num_heads * v_head_dim} columns cannot be normed in {norm_groups} equal parts")
+        if state_size > 256:
+            raise ValueError(f"a state of {state_size} rows is larger than the recurrence kernel takes (256)")
+        self.hidden_size, self.num_heads, self.v_head_dim = int(hidden_size), int(num_heads), int(v_head_dim)
+        self.state_size, self.groups, self.norm_groups = int(state_size), int(groups), int(norm_groups)
+        self.taps, self.norm_eps = int(conv_taps), float(norm_eps)
+        self.inner = self.num_heads * self.v_head_dim
+        self.bc_size = self.groups * self.state_size
+        self.conv_size = self.inner + 2 * self.bc_size
+
+    def tensor_specs(self, prefix):
+        H, nh = self.hidden_size, self.num_heads
+        return [
+            TensorSpec(f"{prefix}.in", (2 * self.inner + 2 * self.bc_size + nh, H), "matrix"),
+            TensorSpec(f"{prefix}.conv", (self.conv_size, self.taps), "vector"),
+            TensorSpec(f"{prefix}.conv.b", (self.conv_size,), "bias"),
+            TensorSpec(f"{prefix}.dt_bias", (nh,), "vector"),
+            TensorSpec(f"{prefix}.A_log", (nh,), "vector"),
+            TensorSpec(f"{prefix}.D", (nh,), "vector"),
+            TensorSpec(f"{prefix}.norm", (self.inner,), "norm"),
+            TensorSpec(f"{prefix}.o", (H, self.inner), "matrix"),
+        ]
+
+    def bind(self, tensors, prefix):
+        self.in_weight = _fused_rows([tensors.pop(f"{prefix}.in")])
+        self.conv_weight, self.conv_bias = tensors[f"{prefix}.conv"], tensors[f"{prefix}.conv.b"]
+        self.dt_bias, self.A_log, self.skip = tensors[f"{prefix}.dt_bias"], tensors[f"{prefix}.A_log"], tensors[f"{prefix}.D"]
+        self.norm_weight, self.o_weight = tensors[f"{prefix}.norm"], tensors[f"{prefix}.o"]
+
+    def cache_need(self):
+        history = FixedState((self.taps - 1, self.conv_size), torch.float32) if self.taps > 1 else None
+        return CombinedNeed((history, FixedState((self.num_heads, self.state_size, self.v_head_dim), torch.float32)))
+
+    def forward(self, x, h, ctx, cache: LayerCache, owns_cache: bool):
+        T = x.shape[0]
+        nh, dv, N, G = self.num_heads, self.v_head_dim, self.state_size, self.groups
+        inner, BC, C = self.inner, self.bc_size, self.conv_size
+        history, state = cache.parts
+        ws = ctx.workspace
+        proj = ws.get("recurrent_in", (T, self.in_weight.shape[0]), ctx.act_dtype)
+        ops.gemm(x, self.in_weight, None, proj)
+        conv = ws.get("recurrent_conv", (T, C), ctx.act_dtype)
+        ops.short_conv(proj[:, inner:inner + C], conv, self.conv_weight, None if history is None else history.state, ctx,
+                       advance=owns_cache, bias=self.conv_bias, residual=False, silu=True)
+        decay, step = ws.get("recurrent_decay", (T, nh), torch.float32), ws.get("recurrent_beta", (T, nh), torch.float32)
+        ops.recurrence_gates(proj, inner + C, None, self.A_log, self.dt_bias, decay, step, nh)
+        o = ws.get("recurrent_out", (T, inner), torch.float32)
+        # q = C, k = B, v = x; the step size multiplies the write
+        ops.gated_recurrence(conv[:, inner + BC:], conv[:, inner:inner + BC], conv[:, :inner], decay, step, o, state.state, ctx,
+                             nh, G, N, dv, delta_rule=False, skip=self.skip, write_state=owns_cache)
+        y = ws.get("recurrent_gated", (T, inner), ctx.act_dtype)
+        ops.gated_group_norm(o, proj[:, :inner], self.norm_weight, self.norm_eps, y, group=inner // self.norm_groups,
+                             gate_kind="silu", gate_first=True)
+        ops.gemm(y, self.o_weight, None, h, accumulate=True)
+
+
+register_part("mixer", "gated_delta_rule", GatedDeltaRule)
+register_part("mixer", "state_space_duality", StateSpaceDuality)

@@ -1,0 +1,97 @@
+"""A layer over several residual streams (hyper-connections), as a block kind.
+
+A token has ``streams`` residual rows x_1 .. x_S instead of one (the model keeps them as [T, S x H] fp32 and starts them
+all from the embedding output; its result is their sum).  For each sublayer (1: the mixer, 2: the feed-forward), with
+three learned tensors ``<hc>.in`` [S], ``<hc>.out`` [S] and ``<hc>.mix`` [S, S] (indexed [from, to]):
+
+  u = sum_s in[s] x_s;   y = sublayer(norm(u));   x_r <- sum_s mix[s, r] x_s + out[r] y     (all r from the old streams)
+
+The read with its RMS norm and the write of the sublayer before it are one pass over the streams
+(``ops.streams_step``).  Mixers and feed-forwards keep their interface: they ADD their result into a zeroed fp32 row
+buffer, which the write then distributes.  A layer may have no feed-forward.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from .base import Block, TensorSpec
+from .plan import register_part
+
+
+class ResidualStreamsBlock(Block):
+    # the model hands this block [T, streams x H] rows
+    def __init__(self, hidden_size: int, mixer, feed_forward, mixer_norm, feed_forward_norm, streams: int,
+                 mixer_prefix: str = "mix", feed_forward_prefix: str = "mlp", mixer_norm_prefix: str = "norm1",
+                 feed_forward_norm_prefix: str = "norm2", mixer_streams_prefix: str = "hc1",
+                 feed_forward_streams_prefix: str = "hc2"):
+        self.hidden_size, self.streams = int(hidden_size), int(streams)
+        if not 1 <= self.streams <= 8:
+            raise ValueError(f"{streams} residual streams (one to eight)")
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
+        for n in (mixer_norm, feed_forward_norm):
+            # the read forms the norm itself: an RMS norm over the whole row with a plain weight
+            if getattr(n, "groups", 1) != 1 or not hasattr(n, "eps") or n.hidden_size != self.hidden_size:
+                raise ValueError("a block over residual streams takes RMS norms over the whole row")
+        self._names = (mixer_prefix, feed_forward_prefix, mixer_norm_prefix, feed_forward_norm_prefix,
+                       mixer_streams_prefix, feed_forward_streams_prefix)
+        self.hc = {}
+
+    def _children(self, prefix):
+        m, f, n1, n2, _, _ = self._names
+        out = [(self.mixer_norm, f"{prefix}.{n1}"), (self.mixer, f"{prefix}.{m}" if m else prefix)]
+        if self.feed_forward is not None:
+            out += [(self.feed_forward_norm, f"{prefix}.{n2}"), (self.feed_forward, f"{prefix}.{f}")]
+        return out
+
+    def _stream_prefixes(self, prefix):
+        out = [f"{prefix}.{self._names[4]}"]
+        if self.feed_forward is not None:
+            out.append(f"{prefix}.{self._names[5]}")
+        return out
+
+    def tensor_specs(self, prefix):
+        S = self.streams
+        out = []
+        for part, p in self._children(prefix):
+            out += part.tensor_specs(p)
+        for p in self._stream_prefixes(prefix):
+            out += [TensorSpec(f"{p}.in", (S,), "vector"), TensorSpec(f"{p}.out", (S,), "vector"),
+                    TensorSpec(f"{p}.mix", (S, S), "vector")]
+        return out
+
+    def bind(self, tensors, prefix):
+        for part, p in self._children(prefix):
+            part.bind(tensors, p)
+        self.hc = [tuple(tensors[f"{p}.{n}"] for n in ("in", "out", "mix")) for p in self._stream_prefixes(prefix)]
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    @property
+    def graph_safe(self):
+        return bool(getattr(self.mixer, "graph_safe", False)
+                    and (self.feed_forward is None or getattr(self.feed_forward, "graph_safe", False)))
+
+    def forward(self, h, ctx, cache, owns_cache):
+        T, S, H = h.shape[0], self.streams, self.hidden_size
+        x = ctx.workspace.get("block_normed", (T, H), ctx.act_dtype)
+        y = ctx.workspace.get("streams_sublayer_out", (T, H), torch.float32)
+        in1, out1, mix1 = self.hc[0]
+        ops.streams_step(h, S, read=(in1, self.mixer_norm.weight, self.mixer_norm.eps, x))
+        y.zero_()
+        self.mixer.forward(x, y, ctx, cache, owns_cache)
+        if self.feed_forward is None:
+            ops.streams_step(h, S, write=(y, mix1, out1))
+            return
+        in2, out2, mix2 = self.hc[1]
+        ops.streams_step(h, S, write=(y, mix1, out1),
+                         read=(in2, self.feed_forward_norm.weight, self.feed_forward_norm.eps, x))
+        y.zero_()
+        self.feed_forward.forward(x, y, ctx)
+        ops.streams_step(h, S, write=(y, mix2, out2))
+
+
+register_part("block", "residual_streams", ResidualStreamsBlock)
