@@ -59,11 +59,9 @@ def plan_nusudra(cfg: NusudraConfig) -> ModelPlan:
                                                "weight_name": "shift", "inner_prefix": "mix"})
         ff = None if layer.ff is None else PartSpec("dense_activation", {
             "hidden_size": W, "intermediate_size": layer.ff, "activation": "relu2"})
-        if cfg.streams is not None:
-            block = PartSpec("residual_streams", {"streams": cfg.streams, "mixer_prefix": ""})
-        else:
-            block = PartSpec("pre_norm_residual", {"mixer_prefix": "", "feed_forward_prefix": "mlp",
-                                                   "mixer_norm_prefix": "norm1", "feed_forward_norm_prefix": "norm2"})
+        # without streams: one stream with in = mix = out = 1, the plain pre-norm residual layer
+        block = PartSpec("residual_streams", {"streams": cfg.streams or 1, "mixer_prefix": "",
+                                              "learned": cfg.streams is not None})
         layers.append(LayerPlan(prefix=f"l{i}", mixer=mixer, feed_forward=ff, mixer_norm=norm, feed_forward_norm=norm,
                                 block=block))
     return ModelPlan(

@@ -8,7 +8,9 @@ three learned tensors ``<hc>.in`` [S], ``<hc>.out`` [S] and ``<hc>.mix`` [S, S] 
 
 The read with its RMS norm and the write of the sublayer before it are one pass over the streams
 (``ops.streams_step``).  Mixers and feed-forwards keep their interface: they ADD their result into a zeroed fp32 row
-buffer, which the write then distributes.  A layer may have no feed-forward.
+buffer, which the write then distributes.  A layer may have no feed-forward.  ``learned`` False (one stream only): no
+stream tensors are read and in = mix = out = 1, which is the plain pre-norm residual layer x <- x + sublayer(norm(x))
+through the same kernels.
 """
 
 from __future__ import annotations
@@ -25,10 +27,12 @@ class ResidualStreamsBlock(Block):
     def __init__(self, hidden_size: int, mixer, feed_forward, mixer_norm, feed_forward_norm, streams: int,
                  mixer_prefix: str = "mix", feed_forward_prefix: str = "mlp", mixer_norm_prefix: str = "norm1",
                  feed_forward_norm_prefix: str = "norm2", mixer_streams_prefix: str = "hc1",
-                 feed_forward_streams_prefix: str = "hc2"):
-        self.hidden_size, self.streams = int(hidden_size), int(streams)
+                 feed_forward_streams_prefix: str = "hc2", learned: bool = True):
+        self.hidden_size, self.streams, self.learned = int(hidden_size), int(streams), bool(learned)
         if not 1 <= self.streams <= 8:
             raise ValueError(f"{streams} residual streams (one to eight)")
+        if not self.learned and self.streams != 1:
+            raise ValueError("streams without learned weights: one stream only")
         self.mixer, self.feed_forward = mixer, feed_forward
         self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
         for n in (mixer_norm, feed_forward_norm):
@@ -57,7 +61,7 @@ class ResidualStreamsBlock(Block):
         out = []
         for part, p in self._children(prefix):
             out += part.tensor_specs(p)
-        for p in self._stream_prefixes(prefix):
+        for p in self._stream_prefixes(prefix) if self.learned else ():
             out += [TensorSpec(f"{p}.in", (S,), "vector"), TensorSpec(f"{p}.out", (S,), "vector"),
                     TensorSpec(f"{p}.mix", (S, S), "vector")]
         return out
@@ -65,7 +69,11 @@ class ResidualStreamsBlock(Block):
     def bind(self, tensors, prefix):
         for part, p in self._children(prefix):
             part.bind(tensors, p)
-        self.hc = [tuple(tensors[f"{p}.{n}"] for n in ("in", "out", "mix")) for p in self._stream_prefixes(prefix)]
+        if self.learned:
+            self.hc = [tuple(tensors[f"{p}.{n}"] for n in ("in", "out", "mix")) for p in self._stream_prefixes(prefix)]
+        else:
+            one = torch.ones(1, dtype=torch.float32, device=self.mixer_norm.weight.device)
+            self.hc = [(one, one, one)] * len(self._stream_prefixes(prefix))
 
     def cache_need(self):
         return self.mixer.cache_need()

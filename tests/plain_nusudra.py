@@ -85,6 +85,28 @@ def rotate_half(x, positions, base, dims):
     return out
 
 
+def decayed_scan(q, k, v, g, S):
+    """Per head: S_t = g_t S_(t-1) + k_t v_t^T, o_t = S_t^T q_t.  q, k [T, H, n]; v [T, H, dv]; g [T, H]; S [H, n, dv]."""
+    S = S.clone()
+    o = torch.zeros(v.shape, dtype=F)
+    for t in range(q.shape[0]):
+        S = g[t][:, None, None] * S + k[t][:, :, None] * v[t][:, None, :]
+        o[t] = torch.einsum("hnv,hn->hv", S, q[t])
+    return o, S
+
+
+def delta_rule_scan(q, k, v, g, beta, S):
+    """Per head: S <- g_t S; u = beta_t (v_t - S^T k_t); S <- S + k_t u^T; o_t = S^T q_t (after the write)."""
+    S = S.clone()
+    o = torch.zeros(v.shape, dtype=F)
+    for t in range(q.shape[0]):
+        S = g[t][:, None, None] * S
+        u = beta[t][:, None] * (v[t] - torch.einsum("hnv,hn->hv", S, k[t]))
+        S = S + k[t][:, :, None] * u[:, None, :]
+        o[t] = torch.einsum("hnv,hn->hv", S, q[t])
+    return o, S
+
+
 # --------------------------------------------------------------------------------------------- mixers
 def latent_attention(h, w, p, m, eps, positions, past=None):
     """``past``: (latents [P, kv_rank], rotated key parts [P, rot_dim]) of the tokens before h[0], or None.
@@ -155,13 +177,10 @@ def state_space(h, w, p, m, eps, past=None):
     C = xbc[:, inner + G * N:].reshape(T, G, N)
     dt = softplus(dt + w[p + ".dt_bias"])  # [T, nh]
     decay = torch.exp(-torch.exp(w[p + ".A_log"]) * dt)
-    S = torch.zeros(nh, N, dv, dtype=F) if past is None else past[0].clone()
+    S = torch.zeros(nh, N, dv, dtype=F) if past is None else past[0]
     group_of = torch.arange(nh) // (nh // G)
-    y = torch.zeros(T, nh, dv, dtype=F)
-    for t in range(T):
-        Bt, Ct = B[t, group_of], C[t, group_of]  # [nh, N]
-        S = decay[t][:, None, None] * S + dt[t][:, None, None] * Bt[:, :, None] * x[t][:, None, :]
-        y[t] = torch.einsum("hnv,hn->hv", S, Ct) + w[p + ".D"][:, None] * x[t]
+    y, S = decayed_scan(C[:, group_of], B[:, group_of], dt[..., None] * x, decay, S)
+    y = y + w[p + ".D"][:, None] * x
     y = y.reshape(T, inner) * silu(z)
     y = rms_div(y.reshape(T, ng, inner // ng), eps).reshape(T, inner) * w[p + ".norm"]
     return y @ w[p + ".o"].T, (S, conv_state)
@@ -187,15 +206,9 @@ def gated_delta(h, w, p, m, eps, past=None):
     k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
     beta = torch.sigmoid(h @ w[p + ".b"].T)  # [T, nh]
     g = torch.exp(-torch.exp(w[p + ".A_log"]) * softplus(h @ w[p + ".a"].T + w[p + ".dt_bias"]))
-    S = torch.zeros(nh, d, dv, dtype=F) if past is None else past[0].clone()
+    S = torch.zeros(nh, d, dv, dtype=F) if past is None else past[0]
     qk_of = torch.arange(nh) // (nh // G)
-    o = torch.zeros(T, nh, dv, dtype=F)
-    for t in range(T):
-        kt, qt = k[t, qk_of], q[t, qk_of]  # [nh, d]
-        S = g[t][:, None, None] * S
-        u = beta[t][:, None] * (v[t] - torch.einsum("hdv,hd->hv", S, kt))
-        S = S + kt[:, :, None] * u[:, None, :]
-        o[t] = torch.einsum("hdv,hd->hv", S, qt)
+    o, S = delta_rule_scan(q[:, qk_of], k[:, qk_of], v, g, beta, S)
     o = rms_div(o, eps) * w[p + ".norm"]
     o = o * silu(h @ w[p + ".g"].T).reshape(T, nh, dv)
     return o.reshape(T, nh * dv) @ w[p + ".o"].T, (S, (cq, ck, cv))
