@@ -556,6 +556,9 @@ def main() -> int:
                     help="instead of the measurement: the Kugilix decoder beside the Qwen2 decoder at equal layer sizes "
                          "(names of bench_designs.SIZES, with commas): prefill and decode through the step function, and "
                          "the Kugilix design's own kernels alone; prints one JSON line of its own")
+    ap.add_argument("--design", default="kugilix", choices=["kugilix", "nusudra"],
+                    help="with --designs: which design is set beside the others (kugilix: beside Qwen2; nusudra: beside "
+                         "Kugilix and Qwen2, with its own kernels alone as well)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -567,8 +570,8 @@ def main() -> int:
         clocks.start()
         sizes = [n for n in args.designs.split(",") if n]
         result = bench_designs.run(build_engine, time_decode, time_prefill, peaks, steps=min(args.steps, 32),
-                                   warmup=max(args.warmup, 3), sizes=sizes, kernels_at=sizes[-1])
-        result.update(metric="two designs at equal layer sizes: prefill and decode tok/s, kernels alone", dtype="bf16",
+                                   warmup=max(args.warmup, 3), sizes=sizes, kernels_at=sizes[-1], design=args.design)
+        result.update(metric="designs at equal layer sizes: prefill and decode tok/s, kernels alone", dtype="bf16",
                       data="synthetic (seeded uniform token ids, random-init weights)", peaks=peak_source,
                       clocks=clocks.stop())
         print(json.dumps(result))

@@ -1,6 +1,7 @@
-"""Two designs side by side at equal layer sizes: the Kugilix decoder beside the Qwen2 dense decoder, random weights.
+"""Designs side by side at equal layer sizes: the Kugilix decoder beside the Qwen2 dense decoder, or (``design`` =
+"nusudra") the Nusudra decoder beside both, random weights.
 
-Called by ``bench.py --designs``.  For each of a few sizes that resemble a real model's layers it measures, through
+Called by ``bench.py --designs [--design nusudra]``.  For each of a few sizes that resemble a real model's layers it measures, through
 the step function, the prefill of one prompt and decode steps at two batch sizes for both designs, and times the
 kernels that only the Kugilix design has (decayed linear attention, the windowed attention with slopes, the short
 convolution, the norms in groups, the gated norm, the activation) alone, with what they reach of the measured copy
@@ -54,6 +55,27 @@ def qwen2_config(s: dict) -> dict:
             "num_key_value_heads": s["kv_heads"], "head_dim": s["dim"], "max_position_embeddings": 8192,
             "rms_norm_eps": 1e-6, "rope_theta": 1e6, "hidden_act": "silu", "tie_word_embeddings": False,
             "use_sliding_window": True, "sliding_window": WINDOW, "max_window_layers": 0}
+
+
+NUSUDRA_ORDER = ("delta", "latent_attention", "parallel")
+
+
+def nusudra_config(s: dict) -> dict:
+    """As many layers as the Kugilix model has layer runs, its three mixers in turn; the same width, heads, head
+    size and feed-forward; four residual streams.  The latent row (192 + 64) is the widest the general attention
+    kernel takes; the state-space layer has as many heads of the same size, a state of 128 and one group."""
+    H, G, d = s["heads"], s["kv_heads"], s["dim"]
+    mixers = {
+        "delta": {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "conv": 4},
+        "latent_attention": {"heads": H, "dim": d, "rot_dim": 64, "vdim": d, "kv_rank": 192,
+                             "scale": 1.0 / math.sqrt(d + 64), "rot": {"base": 10000.0, "dims": 64}},
+        "parallel": {"left": {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "scale": 1.0 / math.sqrt(d)},
+                     "right": {"heads": H, "vdim": d, "state": 128, "groups": 1, "norm_groups": 1, "conv": 4}},
+    }
+    layers = [{"type": NUSUDRA_ORDER[i % 3], "mixer": mixers[NUSUDRA_ORDER[i % 3]], "mlp": {"kind": "dense", "ff": s["ff"]}}
+              for i in range(kugilix_runs(s))]
+    return {"architecture": "Nusudra", "vocab": VOCAB, "width": s["width"], "embedding": {"scale": math.sqrt(s["width"])},
+            "norm": {"eps": 1e-6}, "streams": 4, "layers": layers}
 
 
 def _timed(fn, flush, warmup=3, iters=5, reps=1):
@@ -175,16 +197,144 @@ def kernel_numbers(s: dict, peaks: dict) -> dict:
     return out
 
 
+def nusudra_kernel_numbers(s: dict, peaks: dict) -> dict:
+    """The Nusudra design's own kernels alone at the layer sizes ``s``, measured as ``kernel_numbers`` measures."""
+    import torch
+    from types import SimpleNamespace
+
+    from ferrisinfer_b200.engine.workspace import Workspace
+    from ferrisinfer_b200.kernels import ops
+
+    dev = torch.device("cuda")
+    bf = torch.bfloat16
+    flush = torch.zeros(96 << 20, dtype=torch.float32, device=dev)  # 384 MB
+    W, H, G, d = s["width"], s["heads"], s["kv_heads"], s["dim"]
+    hbm = peaks["hbm_gbs"] * 1e9
+    ws = Workspace(dev)
+    out = {}
+
+    def ctx_of(q_lens, start):
+        S = len(q_lens)
+        q_start = [0]
+        for n in q_lens:
+            q_start.append(q_start[-1] + n)
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+        return SimpleNamespace(num_tokens=q_start[-1], num_seqs=S, max_q_len=max(q_lens), workspace=ws,
+                               max_kv_len=start + max(q_lens),
+                               token_seq=i32([i for i in range(S) for _ in range(q_lens[i])]),
+                               positions=i32([start + j for i in range(S) for j in range(q_lens[i])]),
+                               seq_q_start=i32(q_start), seq_start_pos=i32([start] * S), seq_state_slot=i32(list(range(S))))
+
+    def record(name, seconds, bytes_=None, flops=None):
+        e = {"us": round(seconds * 1e6, 1)}
+        if bytes_ is not None:
+            e["GBps"] = round(bytes_ / seconds / 1e9, 1)
+            e["frac_hbm"] = round(bytes_ / seconds / hbm, 3)
+        if flops is not None:
+            e["TFLOPs_fp32"] = round(flops / seconds / 1e12, 2)
+            e["frac_fp32_nominal"] = round(flops / seconds / (FP32_NOMINAL_TFLOPS * 1e12), 3)
+        out[name] = e
+
+    # ---- the recurrences: delta rule (q/k heads shared by heads / G value heads) and the state-space form (state 128)
+    for form, qk_heads, n, delta in (("delta_rule", G, d, True), ("state_space", 1, 128, False)):
+        for tag, q_lens in (("decode_b64", [1] * 64), ("prefill_2048", [2048])):
+            T, S = sum(q_lens), len(q_lens)
+            q = (torch.randn(T, qk_heads * n, device=dev) / math.sqrt(n)).to(bf)
+            k = (torch.randn(T, qk_heads * n, device=dev) / math.sqrt(n)).to(bf)
+            v = torch.randn(T, H * d, device=dev).to(bf)
+            decay, beta = torch.full((T, H), 0.97, device=dev), torch.full((T, H), 0.5, device=dev)
+            state = torch.zeros(S + 1, H, n, d, device=dev)
+            o = torch.empty(T, H * d, device=dev)
+            ctx = ctx_of(q_lens, 0)
+            t = _timed(lambda: ops.gated_recurrence(q, k, v, decay, beta, o, state, ctx, H, qk_heads, n, d, delta_rule=delta), flush)
+            moved = 2 * S * H * n * d * 4 + T * (2 * qk_heads * n + H * d) * 2 + T * H * d * 4
+            record(f"{form}_{tag}", t, bytes_=moved, flops=(6.0 if delta else 4.0) * T * H * n * d)
+    # ---- attention with a sink and a logarithmic distance penalty (every key is seen), and over the shared latent
+    terms = ops.ScoreTerms(log_r1=torch.full((H,), 0.5, device=dev), log_r2=torch.full((H,), 0.3, device=dev),
+                           sink=torch.zeros(H, device=dev))
+    rank, rot = 192, 64
+    for name, batch, q_len, ctx_len in (("decode_b64", 64, 1, 2048), ("prefill_2048", 1, 2048, 0)):
+        T = batch * q_len
+        pages_each = (ctx_len + q_len + 15) // 16
+        tables = torch.arange(batch * pages_each, dtype=torch.int32, device=dev).view(batch, pages_each)
+        ctx = ctx_of([q_len] * batch, ctx_len)
+        keys = sum(ctx_len + j + 1 for j in range(q_len)) * batch
+        k = torch.randn(batch * pages_each + 1, G, 16, d, device=dev).to(bf)
+        v = torch.randn_like(k)
+        qkv = torch.randn(T, (H + 2 * G) * d, device=dev).to(bf)
+        o = torch.empty(T, H * d, dtype=bf, device=dev)
+        t = _timed(lambda: ops.paged_attention_simt(qkv, o, k, v, tables, ctx.token_seq, ctx.positions, H, G, d, 0,
+                                                    1.0 / math.sqrt(d), score_slopes=terms, v_head_dim=d, max_q_len=q_len,
+                                                    max_kv_len=ctx_len + q_len, workspace=ws), flush)
+        record(f"sink_attention_{name}", t, flops=4.0 * keys * H * d,
+               bytes_=batch * G * (ctx_len + 1) * 2 * d * 2 + T * H * d * 4 if q_len == 1 else None)
+        kl = torch.randn(batch * pages_each + 1, 1, 16, rank + rot, device=dev).to(bf)
+        ql = torch.randn(T, H * (rank + rot), device=dev).to(bf)
+        ol = torch.empty(T, H * rank, dtype=bf, device=dev)
+        t = _timed(lambda: ops.paged_attention_simt(ql, ol, kl, None, tables, ctx.token_seq, ctx.positions, H, 1, rank + rot, 0,
+                                                    0.07, v_head_dim=rank, max_q_len=q_len, max_kv_len=ctx_len + q_len,
+                                                    workspace=ws, values_in_keys=True), flush)
+        record(f"latent_attention_{name}", t, flops=2.0 * keys * H * (2 * rank + rot),
+               bytes_=batch * (ctx_len + 1) * (rank + rot) * 2 + T * H * (2 * rank + rot) * 2 if q_len == 1 else None)
+        # the per-head products around it: plain queries through the key up-projection, latents through the value one
+        x = torch.randn(T, H * (d + rot), device=dev).to(bf)
+        uk = (torch.randn(H, d, rank, device=dev) / math.sqrt(d)).to(bf)
+        t = _timed(lambda: ops.head_gemm(x, d + rot, uk, ql, rank + rot), flush, reps=10 if T <= 64 else 1)
+        record(f"head_product_{name}", t, flops=2.0 * T * H * d * rank, bytes_=H * d * rank * 2 + T * H * (d + rank) * 2)
+        proj = torch.randn(T, H * (d + rot) + rank + rot, device=dev).to(bf)
+        slots = (tables[ctx.token_seq.long(), (ctx.positions // 16).long()] * 16 + ctx.positions % 16).int()
+        freq = torch.full((rot // 2,), 0.01, device=dev)
+        nw = torch.ones(rank, device=dev)
+        t = _timed(lambda: ops.latent_prepare(proj, 0, H * (d + rot), nw, 1e-6, ctx.positions, freq, rot, slots, kl, ql, H, d, rot,
+                                              rank), flush, reps=10 if T <= 64 else 1)
+        record(f"latent_prepare_{name}", t, bytes_=T * (2 * H * rot + 2 * (rank + rot)) * 2)
+    # ---- row-wise kernels of a long step and of a decode step
+    S4 = 4
+    for tag, T in (("2048", 2048), ("b64", 64)):
+        xs = torch.randn(T, S4 * W, device=dev)
+        y = torch.randn(T, W, device=dev)
+        mix, ow, iw, nw = torch.eye(S4, device=dev), torch.ones(S4, device=dev), torch.full((S4,), 0.25, device=dev), torch.ones(W, device=dev)
+        a, b = torch.empty(T, W, dtype=bf, device=dev), torch.empty(T, W, dtype=bf, device=dev)
+        reps = 10 if T <= 64 else 1
+        t = _timed(lambda: ops.streams_step(xs, S4, write=(y, mix, ow), read=(iw, nw, 1e-6, a)), flush, reps=reps)
+        record(f"streams_write_read_{tag}", t, bytes_=T * W * (2 * S4 * 4 + 4 + 2))
+        ctx = ctx_of([T], 0) if T > 64 else ctx_of([1] * T, 5)
+        st = torch.zeros(T + 1, W, device=dev)
+        sh = torch.full((W,), 0.3, device=dev)
+        t = _timed(lambda: ops.token_shift(a, b, sh, st, ctx), flush, reps=reps)
+        record(f"token_shift_{tag}", t, bytes_=T * W * 4 + (T * W * 8 if T <= 64 else 0))
+        C = (2 * G + H) * d
+        wide = torch.randn(T, C + 64, device=dev).to(bf)
+        conv = torch.empty(T, C, dtype=bf, device=dev)
+        cw = torch.randn(C, 4, device=dev) * 0.1
+        cs = torch.zeros(T + 1, 3, C, device=dev)
+        t = _timed(lambda: ops.short_conv(wide[:, :C], conv, cw, cs, ctx, residual=False, silu=True), flush, reps=reps)
+        record(f"conv_silu_{tag}", t, bytes_=T * C * 4 + (ctx.num_seqs * 3 * C * 8 if T <= 64 else 0))
+        o = torch.randn(T, H * d, device=dev)
+        g = torch.randn(T, H * d, device=dev).to(bf)
+        yy = torch.empty(T, H * d, dtype=bf, device=dev)
+        t = _timed(lambda: ops.gated_group_norm(o, g, torch.ones(d, device=dev), 1e-6, yy, group=d, gate_kind="silu"), flush, reps=reps)
+        record(f"gated_head_norm_{tag}", t, bytes_=T * H * d * (4 + 2 + 2))
+        ya, yb = torch.randn(T, W, device=dev), torch.randn(T, W, device=dev)
+        t = _timed(lambda: ops.branch_norm_sum(y, [(ya, nw), (yb, nw)], 0.5, 1e-6), flush, reps=reps)
+        record(f"branch_norm_sum_{tag}", t, bytes_=T * W * 4 * 4)
+    return out
+
+
 def run(build_engine, time_decode, time_prefill, peaks, steps=32, warmup=4, sizes=("small", "1B-like"), context=2048,
-        prompt=2048, batches=(8, 64), kernels_at="1B-like") -> dict:
-    """``build_engine(cfg, batch, context, extra_tokens)``, ``time_decode`` and ``time_prefill`` are bench.py's."""
+        prompt=2048, batches=(8, 64), kernels_at="1B-like", design="kugilix") -> dict:
+    """``build_engine(cfg, batch, context, extra_tokens)``, ``time_decode`` and ``time_prefill`` are bench.py's.
+    ``design`` "kugilix": that design beside Qwen2; "nusudra": that design beside both."""
     import torch
 
     result = {"context": context, "prompt_tokens": prompt, "window": WINDOW, "sizes": {}}
     for name in sizes:
         s = SIZES[name]
         entry = {"layer_sizes": s, "layer_runs": kugilix_runs(s)}
-        for design, cfg in (("kugilix", kugilix_config(s)), ("qwen2", qwen2_config(s))):
+        designs = (("kugilix", kugilix_config(s)), ("qwen2", qwen2_config(s)))
+        if design == "nusudra":
+            designs = (("nusudra", nusudra_config(s)),) + designs
+        for design_name, cfg in designs:
             numbers = {}
             engine = build_engine(cfg, 1, context, extra_tokens=prompt)
             ms = time_prefill(engine, prompt)
@@ -201,8 +351,10 @@ def run(build_engine, time_decode, time_prefill, peaks, steps=32, warmup=4, size
                 numbers[f"decode_b{b}_launches_per_step"] = launches // steps
                 del engine
                 torch.cuda.empty_cache()
-            entry[design] = numbers
+            entry[design_name] = numbers
         result["sizes"][name] = entry
     if kernels_at:
         result["kernels"] = {"at": kernels_at, **kernel_numbers(SIZES[kernels_at], peaks)}
+        if design == "nusudra":
+            result["kernels_nusudra"] = {"at": kernels_at, **nusudra_kernel_numbers(SIZES[kernels_at], peaks)}
     return result

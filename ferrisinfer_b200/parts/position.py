@@ -109,8 +109,9 @@ class LogDistancePenalty(PositionEncoding):
         return None, 0
 
     def tensor_specs(self, prefix):
-        return [TensorSpec(f"{prefix}.{self.r1_name}", (self.num_heads,), "vector"),
-                TensorSpec(f"{prefix}.{self.r2_name}", (self.num_heads,), "vector")]
+        # role "norm": positive numbers of order one (a random folder draws them around one)
+        return [TensorSpec(f"{prefix}.{self.r1_name}", (self.num_heads,), "norm"),
+                TensorSpec(f"{prefix}.{self.r2_name}", (self.num_heads,), "norm")]
 
     def bind(self, tensors, prefix):
         self.r1, self.r2 = tensors[f"{prefix}.{self.r1_name}"], tensors[f"{prefix}.{self.r2_name}"]
