@@ -243,7 +243,7 @@ def nusudra_kernel_numbers(s: dict, peaks: dict) -> dict:
             k = (torch.randn(T, qk_heads * n, device=dev) / math.sqrt(n)).to(bf)
             v = torch.randn(T, H * d, device=dev).to(bf)
             decay, beta = torch.full((T, H), 0.97, device=dev), torch.full((T, H), 0.5, device=dev)
-            state = torch.zeros(S + 1, H, n, d, device=dev)
+            state = torch.zeros(S + 1, H, d, n, device=dev)
             o = torch.empty(T, H * d, device=dev)
             ctx = ctx_of(q_lens, 0)
             t = _timed(lambda: ops.gated_recurrence(q, k, v, decay, beta, o, state, ctx, H, qk_heads, n, d, delta_rule=delta), flush)

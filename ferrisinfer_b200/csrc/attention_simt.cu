@@ -1,4 +1,4 @@
-// Attention over the paged cache, general form: any head size up to 256 (the values' may differ
+// Attention over the paged cache, general form: any head size up to 512 (the values' may differ
 // from the queries' and keys'), any page size, any number of heads and groups, an optional window;
 // fp32 arithmetic throughout whatever the storage type.  One block per (token, query head); the warps of a block split the keys and keep
 // a running maximum, sum and weighted value sum each, merged at the end.
@@ -18,7 +18,7 @@ namespace {
 
 constexpr int ATT_THREADS = 128;
 constexpr int ATT_WARPS = ATT_THREADS / 32;
-constexpr int MAX_PER_LANE = 8;  // head size up to 256
+constexpr int MAX_PER_LANE = 16;  // head size up to 512 (the forms below this one: up to 256)
 
 // What else enters a score and the softmax, per query head (any pointer may be null):
 //   slopes:        s_j += slopes[h] * (j - P), a penalty linear in the distance;
@@ -817,7 +817,7 @@ FERRIS_API int ferris_paged_attention_simt(const void* q, int ldq, void* out, in
             FERRIS_LAUNCH_CHECK();
         }
     }
-    if (d % 8 == 0 && dv % 8 == 0 && aligned && (size_t)AL_GROUPS * (dv + 2) * sizeof(float) <= 48 * 1024) {
+    if (d % 8 == 0 && dv % 8 == 0 && d <= 256 && dv <= 256 && aligned && (size_t)AL_GROUPS * (dv + 2) * sizeof(float) <= 48 * 1024) {
         if (dtype == FERRIS_F32)
             launch_lanes<float>(q, ldq, out, ldo, k_cache, v_cache, block_tables, max_blocks, token_seq, positions, tokens, nh, nkv, d, dv, page_size, window, scale, st, s);
         else

@@ -10,10 +10,13 @@
 // shared by heads / qk_heads value heads each, and may carry one fp32 factor per (token, qk head) each (unit norms:
 // the factor is 1 / |x|, formed in fp32 by the gates kernel, so that the vectors themselves are read once as stored).
 //
-// The columns of S do not depend on one another.  A block owns 32 columns of one (request, head); four lanes share a
-// column, each holding rows sub, sub + 4, ... of it in registers.  Eight tokens' q, k (with their factors), the
-// block's 32 values, g and b stand in shared memory at a time; a token costs each lane 2-3 FMAs per held row and two
-// sums over the four lanes.  Tokens of a request are walked in order from its slot, so a step may hold single tokens,
+// The columns of S do not depend on one another.  4, 8, 16 or 32 lanes (by the head's size) share a column, each
+// holding eight rows of it in registers (rows sub, sub + lanes, ...), and a block of 128 threads owns 32, 16, 8 or 4
+// columns of one (request, head): what a token costs is a chain of dependent steps (decay, the product with k summed
+// over the lanes, the write), so the chain is kept short and the columns are spread over many blocks.  Sixteen tokens'
+// q, k, the block's values, g, b and the factors stand in shared memory at a time, and the next sixteen are on their
+// way into registers meanwhile.  The state lies transposed
+// in memory, [slot, head, vdim, dim], so that the lanes of a column read consecutive floats.  Tokens of a request are walked in order from its slot, so a step may hold single tokens,
 // portions of prompts or both.
 #include <math.h>
 
@@ -22,9 +25,8 @@
 namespace {
 
 constexpr int GR_THREADS = 128;
-constexpr int GR_LANES = 4;                      // lanes that share a column
-constexpr int GR_COLS = GR_THREADS / GR_LANES;   // columns of a block
-constexpr int GR_STAGE = 8;                      // tokens in shared memory at a time
+constexpr int GR_KPL = 8;    // rows of the state that a lane holds
+constexpr int GR_STAGE = 16;  // tokens in shared memory at a time
 constexpr int GR_MAX_DIM = 256;
 
 __device__ __forceinline__ float softplus_g(float v) { return fmaxf(v, 0.0f) + log1pf(expf(-fabsf(v))); }
@@ -71,92 +73,157 @@ __global__ void __launch_bounds__(128) recurrence_gates_kernel(const T* proj, in
     }
 }
 
-template <typename T, int KPL, bool DELTA>  // KPL rows of the state per lane: dim <= 4 * KPL
+// LANES lanes share a column, GR_KPL rows each: dim <= GR_KPL * LANES.  AHEAD: the next tokens are requested into registers
+// while the present ones are worked on (portions of prompts); without it a stage goes straight to shared memory.
+template <typename T, int LANES, bool DELTA, bool AHEAD>
 __global__ void __launch_bounds__(GR_THREADS) gated_recurrence_kernel(
     const T* q, int ldq, const T* k, int ldk, const T* v, int ldv, const float* decay, const float* beta,
     const float* qscale, const float* kscale, const float* __restrict__ skip, float* __restrict__ out, int ldo,
     float* state, const int* __restrict__ seq_q_start, const int* __restrict__ seq_state_slot, int heads, int qk_heads,
     int dim, int vdim, int write_state) {
-    __shared__ float qs[GR_STAGE][4 * KPL];
-    __shared__ float ks[GR_STAGE][4 * KPL];
-    __shared__ float vs[GR_STAGE][GR_COLS];
-    __shared__ float gs[GR_STAGE], bs[GR_STAGE];
+    constexpr int COLS = GR_THREADS / LANES;  // columns of a block
+    constexpr int ROWS = GR_KPL * LANES;      // rows of the state that the lanes of a column hold
+    constexpr int VP = (GR_STAGE * COLS + GR_THREADS - 1) / GR_THREADS;  // values a thread brings per stage
+    __shared__ float qs[GR_STAGE][ROWS];
+    __shared__ float ks[GR_STAGE][ROWS];
+    __shared__ float vs[GR_STAGE][COLS];
+    __shared__ float gs[GR_STAGE], bs[GR_STAGE], fqs[GR_STAGE], fks[GR_STAGE];
     pdl_wait();
     pdl_launch_dependents();
     const int seq = blockIdx.x, head = blockIdx.y;
-    const int tid = threadIdx.x, sub = tid & (GR_LANES - 1), cl = tid >> 2;
-    const int col = blockIdx.z * GR_COLS + cl;
+    const int tid = threadIdx.x, sub = tid % LANES, cl = tid / LANES;
+    const int col = blockIdx.z * COLS + cl;
     const bool active = col < vdim;
     const int qh = head / (heads / qk_heads);
     const int row0 = seq_q_start[seq], row1 = seq_q_start[seq + 1];
     if (row1 <= row0) return;
-    float* S = state + ((size_t)seq_state_slot[seq] * heads + head) * (size_t)dim * vdim;
-    float s[KPL];
+    // the state lies transposed, [slot, head, vdim, dim]: the lanes of a column read consecutive floats
+    float* S = state + (((size_t)seq_state_slot[seq] * heads + head) * vdim + (active ? col : 0)) * (size_t)dim;
+    float s[GR_KPL];
 #pragma unroll
-    for (int i = 0; i < KPL; ++i) {
-        const int kk = sub + GR_LANES * i;
-        s[i] = (active && kk < dim) ? S[(size_t)kk * vdim + col] : 0.0f;
+    for (int i = 0; i < GR_KPL; ++i) {
+        const int kk = sub + LANES * i;
+        s[i] = (active && kk < dim) ? S[kk] : 0.0f;
     }
     // rows of the staged vectors beyond the head's size stay zero
-    for (int i = tid; i < GR_STAGE * 4 * KPL; i += GR_THREADS) (&qs[0][0])[i] = 0.0f, (&ks[0][0])[i] = 0.0f;
+    for (int i = tid; i < GR_STAGE * ROWS; i += GR_THREADS) (&qs[0][0])[i] = 0.0f, (&ks[0][0])[i] = 0.0f;
     const float d_skip = skip ? skip[head] : 0.0f;
+    // A stage's q, k, v and per-token numbers are requested into registers while the stage before it is worked on
+    // (the requests of a stage are all in flight together), and go to shared memory when that one is done.
+    float pq[GR_STAGE][2], pk[GR_STAGE][2], pv[VP], pg = 0.0f, pb = 0.0f, pfq = 1.0f, pfk = 1.0f;
+    auto request = [&](int t0) {
+#pragma unroll
+        for (int r = 0; r < GR_STAGE; ++r) {
+            if (t0 + r >= row1) break;  // a single token's block asks for one row
+            const size_t row = (size_t)(t0 + r);
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int c = tid + j * GR_THREADS;
+                if (c < dim) {
+                    pq[r][j] = to_float(q[row * ldq + (size_t)qh * dim + c]);
+                    pk[r][j] = to_float(k[row * ldk + (size_t)qh * dim + c]);
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < VP; ++j) {
+            const int e = tid + j * GR_THREADS, r = e / COLS, c = e % COLS;
+            const int cc = blockIdx.z * COLS + c;
+            pv[j] = 0.0f;
+            if (e < GR_STAGE * COLS && t0 + r < row1 && cc < vdim) pv[j] = to_float(v[(size_t)(t0 + r) * ldv + (size_t)head * vdim + cc]);
+        }
+        if (tid < GR_STAGE && t0 + tid < row1) {
+            const size_t row = (size_t)(t0 + tid);
+            pg = decay[row * heads + head];
+            pb = beta[row * heads + head];
+            pfq = qscale ? qscale[row * qk_heads + qh] : 1.0f;
+            pfk = kscale ? kscale[row * qk_heads + qh] : 1.0f;
+        }
+    };
+    if (AHEAD) request(row0);
     for (int t0 = row0; t0 < row1; t0 += GR_STAGE) {
         const int n = row1 - t0 < GR_STAGE ? row1 - t0 : GR_STAGE;
         __syncthreads();  // the tokens before are done with (and the zeroing above has landed)
-        for (int i = tid; i < n * dim; i += GR_THREADS) {
-            const int r = i / dim, c = i - r * dim;
-            const size_t row = (size_t)(t0 + r);
-            const float fq = qscale ? qscale[row * qk_heads + qh] : 1.0f;
-            const float fk = kscale ? kscale[row * qk_heads + qh] : 1.0f;
-            qs[r][c] = to_float(q[row * ldq + (size_t)qh * dim + c]) * fq;
-            ks[r][c] = to_float(k[row * ldk + (size_t)qh * dim + c]) * fk;
+        if (!AHEAD) {  // a few tokens a request (a step of single tokens): straight into shared memory
+            for (int i = tid; i < n * dim; i += GR_THREADS) {
+                const int r = i / dim, c = i - r * dim;
+                const size_t row = (size_t)(t0 + r);
+                qs[r][c] = to_float(q[row * ldq + (size_t)qh * dim + c]);
+                ks[r][c] = to_float(k[row * ldk + (size_t)qh * dim + c]);
+            }
+            for (int i = tid; i < n * COLS; i += GR_THREADS) {
+                const int r = i / COLS, c = i - r * COLS;
+                const int cc = blockIdx.z * COLS + c;
+                vs[r][c] = cc < vdim ? to_float(v[(size_t)(t0 + r) * ldv + (size_t)head * vdim + cc]) : 0.0f;
+            }
+            if (tid < n) {
+                const size_t row = (size_t)(t0 + tid);
+                gs[tid] = decay[row * heads + head];
+                bs[tid] = beta[row * heads + head];
+                fqs[tid] = qscale ? qscale[row * qk_heads + qh] : 1.0f;
+                fks[tid] = kscale ? kscale[row * qk_heads + qh] : 1.0f;
+            }
+        } else {
+#pragma unroll
+        for (int r = 0; r < GR_STAGE; ++r) {
+            if (r >= n) break;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int c = tid + j * GR_THREADS;
+                if (c < dim) qs[r][c] = pq[r][j], ks[r][c] = pk[r][j];
+            }
         }
-        for (int i = tid; i < n * GR_COLS; i += GR_THREADS) {
-            const int r = i / GR_COLS, c = i - r * GR_COLS;
-            const int cc = blockIdx.z * GR_COLS + c;
-            vs[r][c] = cc < vdim ? to_float(v[(size_t)(t0 + r) * ldv + (size_t)head * vdim + cc]) : 0.0f;
+#pragma unroll
+        for (int j = 0; j < VP; ++j) {
+            const int e = tid + j * GR_THREADS;
+            if (e < n * COLS) (&vs[0][0])[e] = pv[j];
         }
-        if (tid < n) {
-            gs[tid] = decay[(size_t)(t0 + tid) * heads + head];
-            bs[tid] = beta[(size_t)(t0 + tid) * heads + head];
+        if (tid < GR_STAGE) gs[tid] = pg, bs[tid] = pb, fqs[tid] = pfq, fks[tid] = pfk;
         }
         __syncthreads();
+        if (AHEAD && t0 + GR_STAGE < row1) request(t0 + GR_STAGE);
         for (int r = 0; r < n; ++r) {
-            const float g = gs[r], b = bs[r], vv = vs[r][cl];
-            float u, od = 0.0f;
+            const float g = gs[r], b = bs[r], vv = vs[r][cl], fq = fqs[r], fk = fks[r];
+            float kr[GR_KPL], qr[GR_KPL];
+#pragma unroll
+            for (int i = 0; i < GR_KPL; ++i) kr[i] = ks[r][sub + LANES * i], qr[i] = qs[r][sub + LANES * i];
+            // the factors of q and k are one number a token each: they multiply the sums, not the vectors
+            float uk, od0 = 0.0f, od1 = 0.0f;
             if (DELTA) {
-                float dot = 0.0f;
+                float d0 = 0.0f, d1 = 0.0f;  // two chains, so that the sum waits for half as many dependent FMAs
 #pragma unroll
-                for (int i = 0; i < KPL; ++i) {
-                    s[i] *= g;
-                    dot = fmaf(s[i], ks[r][sub + GR_LANES * i], dot);
+                for (int i = 0; i < GR_KPL; i += 2) {
+                    s[i] *= g, s[i + 1] *= g;
+                    d0 = fmaf(s[i], kr[i], d0), d1 = fmaf(s[i + 1], kr[i + 1], d1);
                 }
-                dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-                dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-                u = b * (vv - dot);
+                float dot = d0 + d1;
 #pragma unroll
-                for (int i = 0; i < KPL; ++i) {
-                    s[i] = fmaf(ks[r][sub + GR_LANES * i], u, s[i]);
-                    od = fmaf(s[i], qs[r][sub + GR_LANES * i], od);
+                for (int o = 1; o < LANES; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                uk = (b * (vv - fk * dot)) * fk;
+#pragma unroll
+                for (int i = 0; i < GR_KPL; i += 2) {
+                    s[i] = fmaf(kr[i], uk, s[i]), s[i + 1] = fmaf(kr[i + 1], uk, s[i + 1]);
+                    od0 = fmaf(s[i], qr[i], od0), od1 = fmaf(s[i + 1], qr[i + 1], od1);
                 }
             } else {
-                u = b * vv;
+                uk = (b * vv) * fk;
 #pragma unroll
-                for (int i = 0; i < KPL; ++i) {
-                    s[i] = fmaf(g, s[i], ks[r][sub + GR_LANES * i] * u);
-                    od = fmaf(s[i], qs[r][sub + GR_LANES * i], od);
+                for (int i = 0; i < GR_KPL; i += 2) {
+                    s[i] = fmaf(g, s[i], kr[i] * uk), s[i + 1] = fmaf(g, s[i + 1], kr[i + 1] * uk);
+                    od0 = fmaf(s[i], qr[i], od0), od1 = fmaf(s[i + 1], qr[i + 1], od1);
                 }
             }
-            od += __shfl_xor_sync(0xffffffffu, od, 1);
-            od += __shfl_xor_sync(0xffffffffu, od, 2);
-            if (sub == 0 && active) out[(size_t)(t0 + r) * ldo + (size_t)head * vdim + col] = fmaf(d_skip, vv, od);
+            float od = od0 + od1;
+#pragma unroll
+            for (int o = 1; o < LANES; o <<= 1) od += __shfl_xor_sync(0xffffffffu, od, o);
+            if (sub == 0 && active) out[(size_t)(t0 + r) * ldo + (size_t)head * vdim + col] = fmaf(d_skip, vv, fq * od);
         }
     }
     if (write_state && active) {
 #pragma unroll
-        for (int i = 0; i < KPL; ++i) {
-            const int kk = sub + GR_LANES * i;
-            if (kk < dim) S[(size_t)kk * vdim + col] = s[i];
+        for (int i = 0; i < GR_KPL; ++i) {
+            const int kk = sub + LANES * i;
+            if (kk < dim) S[kk] = s[i];
         }
     }
 }
@@ -206,24 +273,25 @@ __global__ void __launch_bounds__(256) gated_group_norm_kernel(const float* o, i
     }
 }
 
-template <typename T, bool DELTA>
+template <typename T, bool DELTA, bool AHEAD>
 int launch_recurrence(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv, const float* decay,
                       const float* beta, const float* qscale, const float* kscale, const float* skip, float* out, int ldo,
                       float* state, const int* seq_q_start, const int* seq_state_slot, int seqs, int heads, int qk_heads,
                       int dim, int vdim, int write_state, cudaStream_t s) {
-    const dim3 grid(seqs, heads, (vdim + GR_COLS - 1) / GR_COLS), block(GR_THREADS);
-#define FERRIS_GR_LAUNCH(KPL)                                                                                          \
-    ferris_launch(gated_recurrence_kernel<T, KPL, DELTA>, grid, block, 0, s, (const T*)q, ldq, (const T*)k, ldk,      \
-                  (const T*)v, ldv, decay, beta, qscale, kscale, skip, out, ldo, state, seq_q_start, seq_state_slot,   \
-                  heads, qk_heads, dim, vdim, write_state)
+    const dim3 block(GR_THREADS);
+#define FERRIS_GR_LAUNCH(LANES)                                                                                         \
+    ferris_launch(gated_recurrence_kernel<T, LANES, DELTA, AHEAD>,                                                             \
+                  dim3(seqs, heads, (vdim + GR_THREADS / LANES - 1) / (GR_THREADS / LANES)), block, 0, s, (const T*)q, \
+                  ldq, (const T*)k, ldk, (const T*)v, ldv, decay, beta, qscale, kscale, skip, out, ldo, state,          \
+                  seq_q_start, seq_state_slot, heads, qk_heads, dim, vdim, write_state)
     if (dim <= 32)
-        FERRIS_GR_LAUNCH(8);
+        FERRIS_GR_LAUNCH(4);
     else if (dim <= 64)
-        FERRIS_GR_LAUNCH(16);
+        FERRIS_GR_LAUNCH(8);
     else if (dim <= 128)
-        FERRIS_GR_LAUNCH(32);
+        FERRIS_GR_LAUNCH(16);
     else
-        FERRIS_GR_LAUNCH(64);
+        FERRIS_GR_LAUNCH(32);
 #undef FERRIS_GR_LAUNCH
     FERRIS_LAUNCH_CHECK();
 }
@@ -257,24 +325,29 @@ FERRIS_API int ferris_recurrence_gates(const void* proj, int ld, int dtype, int 
 }
 
 // q, k: [tokens, qk_heads x dim] from their first column, rows ldq / ldk apart; v: [tokens, heads x vdim], rows ldv apart;
-// out: fp32 [tokens, heads x vdim]; state: fp32 [slots, heads, dim, vdim]; skip: fp32 [heads] or null.
+// out: fp32 [tokens, heads x vdim]; state: fp32 [slots, heads, vdim, dim] (transposed); skip: fp32 [heads] or null.
 FERRIS_API int ferris_gated_recurrence(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv, int dtype,
                                        const float* decay, const float* beta, const float* qscale, const float* kscale,
                                        const float* skip, float* out, int ldo, float* state, const int* seq_q_start,
                                        const int* seq_state_slot, int seqs, int heads, int qk_heads, int dim, int vdim,
-                                       int delta_rule, int write_state, void* stream) {
+                                       int delta_rule, int write_state, int longest, void* stream) {
     if (seqs <= 0) return FERRIS_OK;
     if (heads <= 0 || qk_heads <= 0 || heads % qk_heads) FERRIS_REFUSE("recurrence: %d heads over %d q/k heads", heads, qk_heads);
     if (dim <= 0 || dim > GR_MAX_DIM || vdim <= 0) FERRIS_REFUSE("recurrence: heads of %d x %d (at most %d rows)", dim, vdim, GR_MAX_DIM);
-    if (heads > 65535 || (vdim + GR_COLS - 1) / GR_COLS > 65535) FERRIS_REFUSE("recurrence: too many heads or columns for one launch");
+    if (heads > 65535 || (vdim + 3) / 4 > 65535) FERRIS_REFUSE("recurrence: too many heads or columns for one launch");
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == FERRIS_F32)
-        return delta_rule ? launch_recurrence<float, true>(q, ldq, k, ldk, v, ldv, decay, beta, qscale, kscale, skip, out, ldo, state, seq_q_start, seq_state_slot, seqs, heads, qk_heads, dim, vdim, write_state, s)
-                          : launch_recurrence<float, false>(q, ldq, k, ldk, v, ldv, decay, beta, qscale, kscale, skip, out, ldo, state, seq_q_start, seq_state_slot, seqs, heads, qk_heads, dim, vdim, write_state, s);
-    if (dtype == FERRIS_BF16)
-        return delta_rule ? launch_recurrence<bf16, true>(q, ldq, k, ldk, v, ldv, decay, beta, qscale, kscale, skip, out, ldo, state, seq_q_start, seq_state_slot, seqs, heads, qk_heads, dim, vdim, write_state, s)
-                          : launch_recurrence<bf16, false>(q, ldq, k, ldk, v, ldv, decay, beta, qscale, kscale, skip, out, ldo, state, seq_q_start, seq_state_slot, seqs, heads, qk_heads, dim, vdim, write_state, s);
-    FERRIS_REFUSE("recurrence: unknown dtype %d", dtype);
+    if (dtype != FERRIS_F32 && dtype != FERRIS_BF16) FERRIS_REFUSE("recurrence: unknown dtype %d", dtype);
+    const bool ahead = longest > GR_STAGE;  // `longest`: the most tokens a request brings (0: not known)
+#define FERRIS_GR_GO(T, D, A)                                                                                                \
+    return launch_recurrence<T, D, A>(q, ldq, k, ldk, v, ldv, decay, beta, qscale, kscale, skip, out, ldo, state, seq_q_start, \
+                                      seq_state_slot, seqs, heads, qk_heads, dim, vdim, write_state, s)
+    if (dtype == FERRIS_F32) {
+        if (delta_rule) { if (ahead) FERRIS_GR_GO(float, true, true); else FERRIS_GR_GO(float, true, false); }
+        if (ahead) FERRIS_GR_GO(float, false, true); else FERRIS_GR_GO(float, false, false);
+    }
+    if (delta_rule) { if (ahead) FERRIS_GR_GO(bf16, true, true); else FERRIS_GR_GO(bf16, true, false); }
+    if (ahead) FERRIS_GR_GO(bf16, false, true); else FERRIS_GR_GO(bf16, false, false);
+#undef FERRIS_GR_GO
 }
 
 // o: fp32 [rows, n]; gate (may be null), out: the activations' type; w: fp32 [wlen], wlen dividing n.

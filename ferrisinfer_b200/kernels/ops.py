@@ -1035,7 +1035,7 @@ def gated_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: t
                      out: torch.Tensor, state: torch.Tensor, ctx, heads: int, qk_heads: int, dim: int, vdim: int,
                      delta_rule: bool, qscale: Optional[torch.Tensor] = None, kscale: Optional[torch.Tensor] = None,
                      skip: Optional[torch.Tensor] = None, write_state: bool = True):
-    """The recurrence of the step's tokens, request by request from each request's state (fp32 [slots, heads, dim, vdim]):
+    """The recurrence of the step's tokens, request by request from each request's state (fp32 [slots, heads, vdim, dim]: S transposed):
     plain: S <- decay S + k (beta v)^T, o = S^T q + skip v;  delta rule: S <- decay S, u = beta (v - S^T k), S <- S + k u^T,
     o = S^T q.  ``q``, ``k``: [T, qk_heads x dim] (views with contiguous rows; value head h uses q/k head
     h / (heads / qk_heads)), optionally times one fp32 factor per (token, q/k head) each; ``v``: [T, heads x vdim];
@@ -1048,7 +1048,7 @@ def gated_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: t
     _need(decay, "decays", torch.float32)
     _need(beta, "step sizes", torch.float32)
     if (not (T == T1 == T2 == T3) or wq != qk_heads * dim or wk != qk_heads * dim or wv != heads * vdim or wo != heads * vdim
-            or out.dtype != torch.float32 or k.dtype != q.dtype or v.dtype != q.dtype or state.shape[1:] != (heads, dim, vdim)
+            or out.dtype != torch.float32 or k.dtype != q.dtype or v.dtype != q.dtype or state.shape[1:] != (heads, vdim, dim)
             or decay.shape != (T, heads) or beta.shape != (T, heads)):
         raise KernelError(f"recurrence: q {tuple(q.shape)}, k {tuple(k.shape)}, v {tuple(v.shape)}, out {tuple(out.shape)}, "
                           f"state {tuple(state.shape)}")
@@ -1067,7 +1067,8 @@ def gated_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: t
                                        _ptr(skip), _ptr(out), _c_int(ldo), _ptr(state), _ptr(ctx.seq_q_start),
                                        _ptr(ctx.seq_state_slot), _c_int(ctx.num_seqs), _c_int(heads), _c_int(qk_heads),
                                        _c_int(dim), _c_int(vdim), _c_int(1 if delta_rule else 0),
-                                       _c_int(1 if write_state else 0), _stream()),
+                                       _c_int(1 if write_state else 0), _c_int(int(getattr(ctx, "max_q_len", 0) or T)),
+                                       _stream()),
         "gated recurrence",
     )
 

@@ -38,8 +38,8 @@ class LatentAttention(Mixer):
         self.norm_eps, self.output_gate = float(norm_eps), bool(output_gate)
         self.q_size = self.num_heads * (self.head_dim + self.rot)
         self.row = self.rank + self.rot  # a token's cache row, and the size of a head's query in the attention
-        if self.row > 256:
-            raise ValueError(f"cache rows of {self.row} are larger than the attention kernel takes (256)")
+        if self.row > 512:
+            raise ValueError(f"cache rows of {self.row} are larger than the attention kernel takes (512)")
         self._freq = {}
 
     def tensor_specs(self, prefix):

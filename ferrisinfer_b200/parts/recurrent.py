@@ -14,7 +14,7 @@
   h += (rmsnorm_in_groups(o * SiLU(z)) * n) Wo^T       the gate before the norm, ``norm_groups`` equal parts.
 
 Both hold all input matrices as one, so that one product feeds the convolution, the gates and the recurrence; the
-state ([heads, dim, vdim] fp32) and the convolution's last taps - 1 inputs are carried in the request's slot, so a
+state (S transposed, [heads, vdim, dim] fp32) and the convolution's last taps - 1 inputs are carried in the request's slot, so a
 sequence may be cut anywhere.  Decays, step sizes, unit norms, the recurrence and the norms are fp32 whatever the
 activations' type.
 """
@@ -82,7 +82,7 @@ class GatedDeltaRule(Mixer):
 
     def cache_need(self):
         history = FixedState((self.taps - 1, self.conv_size), torch.float32) if self.taps > 1 else None
-        return CombinedNeed((history, FixedState((self.num_heads, self.head_dim, self.v_head_dim), torch.float32)))
+        return CombinedNeed((history, FixedState((self.num_heads, self.v_head_dim, self.head_dim), torch.float32)))
 
     def forward(self, x, h, ctx, cache: LayerCache, owns_cache: bool):
         T = x.shape[0]
@@ -147,7 +147,7 @@ class StateSpaceDuality(Mixer):
 
     def cache_need(self):
         history = FixedState((self.taps - 1, self.conv_size), torch.float32) if self.taps > 1 else None
-        return CombinedNeed((history, FixedState((self.num_heads, self.state_size, self.v_head_dim), torch.float32)))
+        return CombinedNeed((history, FixedState((self.num_heads, self.v_head_dim, self.state_size), torch.float32)))
 
     def forward(self, x, h, ctx, cache: LayerCache, owns_cache: bool):
         T = x.shape[0]

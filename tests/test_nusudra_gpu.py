@@ -212,7 +212,7 @@ def test_recurrence_whole_in_portions_and_token_by_token(device, heads, qk_heads
     want = want.reshape(T, heads * vdim)
     dev = lambda t: t.to(device)
     for cuts in ([T], [7, 1, 20, 2, 15], [1] * T):
-        state = torch.randn(3, heads, dim, vdim, device=device)
+        state = torch.randn(3, heads, vdim, dim, device=device)
         state[2] = 0.0
         pos = 0
         for n in cuts:
@@ -224,7 +224,7 @@ def test_recurrence_whole_in_portions_and_token_by_token(device, heads, qk_heads
                                  skip=None if delta else dev(skip))
             assert torch.allclose(out.cpu().double(), want[sl], atol=2e-4, rtol=2e-4), (cuts[:3], pos)
             pos += n
-        assert torch.allclose(state[2].cpu().double(), last, atol=2e-4, rtol=2e-4)
+        assert torch.allclose(state[2].cpu().double().transpose(1, 2), last, atol=2e-4, rtol=2e-4)  # S lies transposed
 
 
 def test_recurrence_of_several_requests_keeps_their_states_apart(device):
@@ -241,7 +241,7 @@ def test_recurrence_of_several_requests_keeps_their_states_apart(device):
                                      v.double().view(n, heads, vdim), decay.double(), beta.double(),
                                      torch.zeros(heads, dim, vdim, dtype=F64))
         want.append(o.reshape(n, heads * vdim))
-    state = torch.zeros(6, heads, dim, vdim, device=device)
+    state = torch.zeros(6, heads, vdim, dim, device=device)
     slots = [4, 1, 5, 0]
     done = [0, 0, 0, 0]
     for step in ([17, 1, 1, 33], [13, 1, 0, 17], [0, 10, 8, 0]):
@@ -280,7 +280,7 @@ def test_recurrence_keeps_a_write_from_hundreds_of_tokens_ago(device):
     want, _ = plain.decayed_scan(q.double().view(T, 1, dim), k.double().view(T, 1, dim), v.double().view(T, 1, vdim),
                                  decay.double(), torch.zeros(1, dim, vdim, dtype=F64))
     assert torch.allclose(want[T - 1, 0], 0.999 ** (T - 4) * v[3].double(), atol=1e-9)
-    state = torch.zeros(1, heads, dim, vdim, device=device)
+    state = torch.zeros(1, heads, vdim, dim, device=device)
     pos, outs = 0, []
     dev = lambda t: t.to(device)
     for n in [64] * 10 + [1] * 64:
@@ -474,7 +474,8 @@ def test_attention_with_a_sink_against_the_plain_mixer(device, nh, nkv, d, dv, d
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
-@pytest.mark.parametrize("nh,d,r,dv,rank,dims", [(4, 16, 16, 24, 48, 16), (3, 24, 8, 40, 32, 4), (8, 8, 8, 8, 16, 8), (2, 64, 32, 64, 96, 32)])
+@pytest.mark.parametrize("nh,d,r,dv,rank,dims", [(4, 16, 16, 24, 48, 16), (3, 24, 8, 40, 32, 4), (8, 8, 8, 8, 16, 8), (2, 64, 32, 64, 96, 32),
+                                                 (2, 32, 32, 32, 320, 32)])  # a row of 352: beyond what the wide-load forms take
 def test_attention_over_a_shared_latent_against_the_plain_mixer(device, nh, d, r, dv, rank, dims, dtype):
     """Norm of the latent, rotation of the shared key part and of the heads' query parts, the cache row, the plain
     queries through the key up-projection, attention whose keys carry the values, the value up-projection with the

@@ -63,7 +63,7 @@ def test_cache_needs_of_the_three_mixers():
     _, _, model = build(cases.CASE_A)
     delta, latent, parallel = (leaf_needs(n) for n in model.cache_needs())
     W = cases.CASE_A["width"]
-    assert delta == [FixedState((W,)), FixedState((3, 2 * 64 + 64)), FixedState((4, 32, 16))]
+    assert delta == [FixedState((W,)), FixedState((3, 2 * 64 + 64)), FixedState((4, 16, 32))]
     assert latent == [FixedState((W,)), PagedKV(1, 48 + 16, None, 0)]  # one shared row a token, no value rows
     assert parallel == [FixedState((W,)), PagedKV(2, 32, None, None), FixedState((3, 64 + 2 * 32)), FixedState((4, 16, 16))]
     _, _, model = build(cases.CASE_C)  # one tap: the convolution keeps nothing
