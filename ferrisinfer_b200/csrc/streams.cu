@@ -47,7 +47,9 @@ template <typename T>
 __global__ void __launch_bounds__(256) streams_step_kernel(float* xs, const float* y, const float* __restrict__ mix,
                                                            const float* __restrict__ out_w, const float* __restrict__ in_w,
                                                            const float* __restrict__ norm_w, float eps, T* __restrict__ out,
-                                                           int streams, int width) {
+                                                           int streams, int width, const float* __restrict__ shift,
+                                                           float* shift_state, const int* __restrict__ positions,
+                                                           const int* __restrict__ seq_state_slot) {
     extern __shared__ float u_row[];  // [width], the read's sum (only with a read)
     __shared__ float scratch[33];
     __shared__ StreamWeights sw;
@@ -98,7 +100,20 @@ __global__ void __launch_bounds__(256) streams_step_kernel(float* xs, const floa
     if (!reads) return;
     ss = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / (float)width + eps);
-    for (int c = threadIdx.x; c < width; c += blockDim.x) out[(size_t)t * width + c] = from_float<T>((u_row[c] * inv) * norm_w[c]);
+    if (!shift) {
+        for (int c = threadIdx.x; c < width; c += blockDim.x) out[(size_t)t * width + c] = from_float<T>((u_row[c] * inv) * norm_w[c]);
+        return;
+    }
+    // A step of single tokens (row t is request t's only token): the token shift of the normed row right here, from and
+    // to the request's state, on the row as it is rounded for the mixer (what the kernels of its own do as well).
+    const int pos = positions[t];
+    float* st = shift_state + (size_t)seq_state_slot[t] * width;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const float own = to_float(from_float<T>((u_row[c] * inv) * norm_w[c]));
+        const float prev = pos == 0 ? 0.0f : st[c];
+        st[c] = own;
+        out[(size_t)t * width + c] = from_float<T>(fmaf(prev - own, shift[c], own));
+    }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -155,7 +170,8 @@ struct Branches {
     int n;
 };
 
-__global__ void __launch_bounds__(256) branch_norm_sum_kernel(Branches br, float coef, float eps, float* h, int width) {
+__global__ void __launch_bounds__(256) branch_norm_sum_kernel(Branches br, float coef, float eps, float* h, int width,
+                                                              int accumulate) {
     __shared__ float scratch[33];
     pdl_wait();
     pdl_launch_dependents();
@@ -179,7 +195,7 @@ __global__ void __launch_bounds__(256) branch_norm_sum_kernel(Branches br, float
 #pragma unroll
         for (int b = 0; b < 4; ++b)
             if (b < br.n) a += (br.y[b][(size_t)t * width + c] * inv[b]) * br.w[b][c];
-        h[(size_t)t * width + c] += coef * a;
+        h[(size_t)t * width + c] = accumulate ? fmaf(coef, a, h[(size_t)t * width + c]) : coef * a;
     }
 }
 
@@ -302,26 +318,30 @@ FERRIS_API int ferris_streams_sum(const float* xs, float* h, int tokens, int str
 }
 
 // xs: fp32 [tokens, streams, width]; y (null: no write): fp32 [tokens, width] with mix [streams, streams] and out_w
-// [streams]; norm_w (null: no read): fp32 [width] with in_w [streams], out: [tokens, width] of `dtype`.
+// [streams]; norm_w (null: no read): fp32 [width] with in_w [streams], out: [tokens, width] of `dtype`.  shift (null: none;
+// only where every request brings one token, row t being request t's): fp32 [width]; the read's rows are shifted towards
+// shift_state[seq_state_slot[t]] (fp32 [slots, width]; zeros at position 0), which takes the unshifted row.
 FERRIS_API int ferris_streams_step(float* xs, const float* y, const float* mix, const float* out_w, const float* in_w,
                                    const float* norm_w, float eps, void* out, int dtype, int tokens, int streams, int width,
+                                   const float* shift, float* shift_state, const int* positions, const int* seq_state_slot,
                                    void* stream) {
     if (tokens <= 0) return FERRIS_OK;
     if (streams <= 0 || streams > MAX_STREAMS || width <= 0) FERRIS_REFUSE("streams: %d streams (at most %d) of %d", streams, MAX_STREAMS, width);
     if (y && (!mix || !out_w)) FERRIS_REFUSE("streams: a write needs its mixing matrix and output weights");
     if (norm_w && (!in_w || !out)) FERRIS_REFUSE("streams: a read needs its input weights and an output");
     if (!y && !norm_w) return FERRIS_OK;
+    if (shift && (!norm_w || !shift_state || !positions || !seq_state_slot)) FERRIS_REFUSE("streams: a token shift goes with a read, a state and the step's positions and slots");
     const size_t smem = norm_w ? (size_t)width * sizeof(float) : 0;
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid(tokens), block(width >= 1024 ? 256 : 128);
     if (dtype == FERRIS_F32) {
         int e_ = ferris_allow_dynamic_smem((const void*)streams_step_kernel<float>, smem);
         if (e_ != FERRIS_OK) return e_;
-        ferris_launch(streams_step_kernel<float>, grid, block, smem, s, xs, y, mix, out_w, in_w, norm_w, eps, (float*)out, streams, width);
+        ferris_launch(streams_step_kernel<float>, grid, block, smem, s, xs, y, mix, out_w, in_w, norm_w, eps, (float*)out, streams, width, shift, shift_state, positions, seq_state_slot);
     } else if (dtype == FERRIS_BF16) {
         int e_ = ferris_allow_dynamic_smem((const void*)streams_step_kernel<bf16>, smem);
         if (e_ != FERRIS_OK) return e_;
-        ferris_launch(streams_step_kernel<bf16>, grid, block, smem, s, xs, y, mix, out_w, in_w, norm_w, eps, (bf16*)out, streams, width);
+        ferris_launch(streams_step_kernel<bf16>, grid, block, smem, s, xs, y, mix, out_w, in_w, norm_w, eps, (bf16*)out, streams, width, shift, shift_state, positions, seq_state_slot);
     } else
         FERRIS_REFUSE("streams: unknown dtype %d", dtype);
     FERRIS_LAUNCH_CHECK();
@@ -356,15 +376,16 @@ FERRIS_API int ferris_token_shift(const void* x, void* out, int dtype, const flo
     FERRIS_LAUNCH_CHECK();
 }
 
-// h fp32 [tokens, width] += coef * sum_b rmsnorm(y_b) * w_b; y_b fp32 [tokens, width], w_b fp32 [width]; 1..4 branches.
+// h fp32 [tokens, width] += (accumulate) or = coef * sum_b rmsnorm(y_b) * w_b; y_b fp32 [tokens, width], w_b fp32 [width];
+// 1..4 branches.
 FERRIS_API int ferris_branch_norm_sum(const float* const* ys, const float* const* ws, int branches, float coef, float eps,
-                                      float* h, int tokens, int width, void* stream) {
+                                      float* h, int tokens, int width, int accumulate, void* stream) {
     if (tokens <= 0) return FERRIS_OK;
     if (branches < 1 || branches > 4 || width <= 0) FERRIS_REFUSE("branch norm: %d branches of %d", branches, width);
     Branches br = {};
     br.n = branches;
     for (int b = 0; b < branches; ++b) br.y[b] = ys[b], br.w[b] = ws[b];
-    ferris_launch(branch_norm_sum_kernel, dim3(tokens), dim3(width >= 1024 ? 256 : 128), 0, (cudaStream_t)stream, br, coef, eps, h, width);
+    ferris_launch(branch_norm_sum_kernel, dim3(tokens), dim3(width >= 1024 ? 256 : 128), 0, (cudaStream_t)stream, br, coef, eps, h, width, accumulate);
     FERRIS_LAUNCH_CHECK();
 }
 

@@ -1119,11 +1119,14 @@ def streams_sum(xs: torch.Tensor, h: torch.Tensor, streams: int):
     _check(_lib().ferris_streams_sum(_ptr(xs), _ptr(h), _c_int(T), _c_int(streams), _c_int(W), _stream()), "streams sum")
 
 
-def streams_step(xs: torch.Tensor, streams: int, write: Optional[tuple] = None, read: Optional[tuple] = None):
+def streams_step(xs: torch.Tensor, streams: int, write: Optional[tuple] = None, read: Optional[tuple] = None,
+                 shift: Optional[tuple] = None):
     """One pass over every token's residual streams (xs fp32 [T, streams x W]): ``write`` = (y fp32 [T, W], mix fp32
     [streams, streams] indexed [from, to], out fp32 [streams]): x_r <- sum_s mix[s, r] x_s + out[r] y, all r from the
     old streams; then ``read`` = (in fp32 [streams], norm weight fp32 [W], eps, out [T, W] in the activations' type):
-    out = rmsnorm(sum_s in[s] x_s) * weight.  Either may be None."""
+    out = rmsnorm(sum_s in[s] x_s) * weight.  Either may be None.  ``shift`` = (weights fp32 [W], state fp32 [slots, W],
+    ctx), only in a step where every request brings one token: the read's rows are token-shifted on their way out, as
+    ``token_shift`` does, from and to the requests' states."""
     _need(xs, "residual streams", torch.float32)
     T = xs.shape[0]
     if xs.dim() != 2 or xs.shape[1] % streams:
@@ -1145,10 +1148,19 @@ def streams_step(xs: torch.Tensor, streams: int, write: Optional[tuple] = None, 
         _need(out, "normed rows")
         if in_w.numel() != streams or norm_w.numel() != W or out.shape != (T, W):
             raise KernelError(f"streams read: in {tuple(in_w.shape)}, norm {tuple(norm_w.shape)}, out {tuple(out.shape)}")
+    sw = sstate = spos = sslot = None
+    if shift is not None:
+        sw, sstate, ctx = shift
+        _need(sw, "token shift weights", torch.float32)
+        _need(sstate, "token shift state", torch.float32)
+        if read is None or sw.numel() != W or sstate.dim() != 2 or sstate.shape[1] != W or ctx.max_q_len != 1 \
+                or ctx.num_seqs != T:
+            raise KernelError("streams step: a token shift goes with a read in a step of single tokens")
+        spos, sslot = ctx.positions, ctx.seq_state_slot
     _check(
         _lib().ferris_streams_step(_ptr(xs), _ptr(y), _ptr(mix), _ptr(out_w), _ptr(in_w), _ptr(norm_w), _c_float(eps),
                                    _ptr(out), _c_int(_dt(out, "normed rows") if out is not None else F32), _c_int(T),
-                                   _c_int(streams), _c_int(W), _stream()),
+                                   _c_int(streams), _c_int(W), _ptr(sw), _ptr(sstate), _ptr(spos), _ptr(sslot), _stream()),
         "streams step",
     )
 
@@ -1173,8 +1185,9 @@ def token_shift(x: torch.Tensor, out: torch.Tensor, shift: torch.Tensor, state: 
     )
 
 
-def branch_norm_sum(h: torch.Tensor, branches: list, coef: float, eps: float):
-    """h += coef * sum_b rmsnorm(y_b) * w_b over ``branches`` = [(y_b fp32 [T, W], w_b fp32 [W]), ...] (one to four)."""
+def branch_norm_sum(h: torch.Tensor, branches: list, coef: float, eps: float, accumulate: bool = True):
+    """h += coef * sum_b rmsnorm(y_b) * w_b over ``branches`` = [(y_b fp32 [T, W], w_b fp32 [W]), ...] (one to four);
+    without ``accumulate`` the sum replaces what h held."""
     _need(h, "residual rows", torch.float32)
     n = len(branches)
     ys = (ctypes.c_void_p * n)()
@@ -1186,7 +1199,7 @@ def branch_norm_sum(h: torch.Tensor, branches: list, coef: float, eps: float):
             raise KernelError(f"branch norm: y {tuple(y.shape)}, w {tuple(w.shape)} for h {tuple(h.shape)}")
         ys[i], ws[i] = y.data_ptr(), w.data_ptr()
     _check(_lib().ferris_branch_norm_sum(ys, ws, _c_int(n), _c_float(coef), _c_float(eps), _ptr(h), _c_int(h.shape[0]),
-                                         _c_int(h.shape[1]), _stream()), "branch norm sum")
+                                         _c_int(h.shape[1]), _c_int(1 if accumulate else 0), _stream()), "branch norm sum")
 
 
 def latent_prepare(proj: torch.Tensor, q_off: int, dkv_off: int, norm_weight: torch.Tensor, eps: float,

@@ -41,6 +41,7 @@ from .plan import PartSpec, build_part, register_part
 
 class GroupedQueryAttention(Mixer):
     accepts_lazy_norm = True  # x goes to ops.gemm and nowhere else
+    can_overwrite = True
 
     @property
     def graph_safe(self):
@@ -137,7 +138,7 @@ class GroupedQueryAttention(Mixer):
                        None if self.v_head_dim == self.head_dim else self.v_head_dim)
 
     # ------------------------------------------------------------------ forward
-    def forward(self, x, h, ctx, cache: LayerCache, owns_cache: bool):
+    def forward(self, x, h, ctx, cache: LayerCache, owns_cache: bool, accumulate: bool = True):
         T = x.shape[0]
         nh, nkv, d = self.num_heads, self.num_kv_heads, self.head_dim
         meta = ctx.paged[cache.group]
@@ -153,7 +154,7 @@ class GroupedQueryAttention(Mixer):
                                    log_r1=None if log is None else log[0], log_r2=None if log is None else log[1])
             ops.paged_attention(qkv, out, cache.k, cache.v, meta.block_tables, ctx, nh, nkv, d, self.window or 0,
                                 self.scale, score_slopes=terms, v_head_dim=dv)
-            ops.gemm(out, self.o_weight, None, h, accumulate=True)
+            ops.gemm(out, self.o_weight, None, h, accumulate=accumulate)
             return
         table = self.position.rotary_table(qkv.device)
         inv_freq, rotary = table if table is not None else (None, 0)
@@ -175,7 +176,7 @@ class GroupedQueryAttention(Mixer):
         attended = ops.attention_step(qkv, out, cache.k, cache.v, meta, ctx, nh, nkv, d, inv_freq, rotary,
                                       self.window or 0, self.scale, write_kv=owns_cache, lazy_merge=True,
                                       rotated=fused, score_slopes=slopes)
-        ops.gemm(attended, self.o_weight, None, h, accumulate=True)
+        ops.gemm(attended, self.o_weight, None, h, accumulate=accumulate)
 
 
 register_part("mixer", "gqa_attention", GroupedQueryAttention)

@@ -230,6 +230,9 @@ class Mixer(Part):
     # loops over requests, no synchronisation, no read of ``ctx.seqs``), so that a step can be recorded into
     # a CUDA graph.  One part that says False switches graphs off for the whole model.
     graph_safe = False
+    # True if forward takes ``accumulate=False``: the result then REPLACES what ``h`` holds (h = mix(x)), which spares
+    # a caller that wants the result alone (a block over several residual streams, mixers side by side) the zeroing.
+    can_overwrite = False
 
     def cache_need(self):
         """PagedKV, FixedState, a CombinedNeed of several, or None."""
@@ -244,6 +247,7 @@ class Mixer(Part):
 class FeedForward(Part):
     accepts_lazy_norm = False  # as for Mixer
     graph_safe = False  # as for Mixer
+    can_overwrite = False  # as for Mixer
 
     def forward(self, x: torch.Tensor, h: torch.Tensor, ctx: StepContext) -> None:
         """h += feed_forward(x)."""

@@ -54,6 +54,7 @@ class DenseActivation(FeedForward):
 
     accepts_lazy_norm = True
     graph_safe = True
+    can_overwrite = True
 
     def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "xielu",
                  up_name: str = "up", down_name: str = "down", act_name: str = "act"):
@@ -82,11 +83,11 @@ class DenseActivation(FeedForward):
             sp = torch.nn.functional.softplus(self.act.detach().to("cpu", torch.float32), threshold=20.0)
             self.coefficients = (float(sp[0]), 0.5 + float(sp[1]))
 
-    def forward(self, x, h, ctx):
+    def forward(self, x, h, ctx, accumulate: bool = True):
         T, I = x.shape[0], self.intermediate_size
         z = ctx.workspace.get("ffn_act", (T, I), ctx.act_dtype)
         ops.gemm_activation(x, self.up, z, self.activation, self.coefficients, self.act)
-        ops.gemm(z, self.down, None, h, accumulate=True)
+        ops.gemm(z, self.down, None, h, accumulate=accumulate)
 
 
 register_part("feed_forward", "swiglu", SwiGLU)

@@ -25,6 +25,7 @@ from .recurrent import _fused_rows
 class LatentAttention(Mixer):
     accepts_lazy_norm = True
     graph_safe = True
+    can_overwrite = True
 
     def __init__(self, hidden_size: int, num_heads: int, head_dim: int, rotary_head_dim: int, v_head_dim: int,
                  latent_rank: int, scale: float, rotary_base: float, rotary_dims: int, norm_eps: float,
@@ -79,7 +80,7 @@ class LatentAttention(Mixer):
             self._freq[key] = torch.tensor(f, dtype=torch.float64).to(torch.float32).to(device)
         return self._freq.get(key)
 
-    def forward(self, x, h, ctx, cache: LayerCache, owns_cache: bool):
+    def forward(self, x, h, ctx, cache: LayerCache, owns_cache: bool, accumulate: bool = True):
         T = x.shape[0]
         nh, d, r, dv, rank, row = self.num_heads, self.head_dim, self.rot, self.v_head_dim, self.rank, self.row
         ws = ctx.workspace
@@ -97,7 +98,7 @@ class LatentAttention(Mixer):
         out = ws.get("latent_out", (T, nh * dv), ctx.act_dtype)
         gate = proj[:, self.q_size + row:self.q_size + row + nh] if self.output_gate else None
         ops.head_gemm(mixed, rank, self.uv, out, dv, gate=gate)
-        ops.gemm(out, self.o_weight, None, h, accumulate=True)
+        ops.gemm(out, self.o_weight, None, h, accumulate=accumulate)
 
 
 register_part("mixer", "latent_attention", LatentAttention)

@@ -17,6 +17,7 @@ import torch
 from ..kernels import ops
 from .base import LayerCache, StepContext
 from .plan import LayerPlan, ModelPlan, build_part
+from .residual_streams import flush_pending_write
 
 
 class DecoderModel:
@@ -113,9 +114,11 @@ class DecoderModel:
                 ops.add_(h, embedded)
             self.blocks[step.layer].forward(h, ctx, caches[owner], owns_cache=step.cache_of is None)
             if self.after_run is not None:
+                flush_pending_write(ctx, h, S)
                 if S > 1:
                     ops.streams_sum(h, row, S)
                 self.after_run(i, row)
+        flush_pending_write(ctx, h, S)  # what the last layer of a block kind over residual streams left undone
         if logits_index is None or logits_index.numel() == 0:
             return None
         if S > 1:

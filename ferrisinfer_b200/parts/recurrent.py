@@ -41,6 +41,7 @@ def _fused_rows(parts: list) -> torch.Tensor:
 class GatedDeltaRule(Mixer):
     accepts_lazy_norm = True
     graph_safe = True
+    can_overwrite = True
 
     def __init__(self, hidden_size: int, num_heads: int, num_qk_heads: int, head_dim: int, v_head_dim: int,
                  conv_taps: int, norm_eps: float, unit_norm_eps: float = 1e-6):
@@ -84,7 +85,7 @@ class GatedDeltaRule(Mixer):
         history = FixedState((self.taps - 1, self.conv_size), torch.float32) if self.taps > 1 else None
         return CombinedNeed((history, FixedState((self.num_heads, self.v_head_dim, self.head_dim), torch.float32)))
 
-    def forward(self, x, h, ctx, cache: LayerCache, owns_cache: bool):
+    def forward(self, x, h, ctx, cache: LayerCache, owns_cache: bool, accumulate: bool = True):
         T = x.shape[0]
         nh, g, d, dv = self.num_heads, self.num_qk_heads, self.head_dim, self.v_head_dim
         QK, V, C = self.qk_size, self.v_size, self.conv_size
@@ -104,12 +105,13 @@ class GatedDeltaRule(Mixer):
                              delta_rule=True, qscale=qscale, kscale=kscale, write_state=owns_cache)
         y = ws.get("recurrent_gated", (T, V), ctx.act_dtype)
         ops.gated_group_norm(o, proj[:, C:C + V], self.norm_weight, self.norm_eps, y, group=dv, gate_kind="silu")
-        ops.gemm(y, self.o_weight, None, h, accumulate=True)
+        ops.gemm(y, self.o_weight, None, h, accumulate=accumulate)
 
 
 class StateSpaceDuality(Mixer):
     accepts_lazy_norm = True
     graph_safe = True
+    can_overwrite = True
 
     def __init__(self, hidden_size: int, num_heads: int, v_head_dim: int, state_size: int, groups: int, norm_groups: int,
                  conv_taps: int, norm_eps: float):
@@ -149,7 +151,7 @@ class StateSpaceDuality(Mixer):
         history = FixedState((self.taps - 1, self.conv_size), torch.float32) if self.taps > 1 else None
         return CombinedNeed((history, FixedState((self.num_heads, self.v_head_dim, self.state_size), torch.float32)))
 
-    def forward(self, x, h, ctx, cache: LayerCache, owns_cache: bool):
+    def forward(self, x, h, ctx, cache: LayerCache, owns_cache: bool, accumulate: bool = True):
         T = x.shape[0]
         nh, dv, N, G = self.num_heads, self.v_head_dim, self.state_size, self.groups
         inner, BC, C = self.inner, self.bc_size, self.conv_size
@@ -169,7 +171,7 @@ class StateSpaceDuality(Mixer):
         y = ws.get("recurrent_gated", (T, inner), ctx.act_dtype)
         ops.gated_group_norm(o, proj[:, :inner], self.norm_weight, self.norm_eps, y, group=inner // self.norm_groups,
                              gate_kind="silu", gate_first=True)
-        ops.gemm(y, self.o_weight, None, h, accumulate=True)
+        ops.gemm(y, self.o_weight, None, h, accumulate=accumulate)
 
 
 register_part("mixer", "gated_delta_rule", GatedDeltaRule)

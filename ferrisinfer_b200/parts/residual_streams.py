@@ -7,8 +7,10 @@ three learned tensors ``<hc>.in`` [S], ``<hc>.out`` [S] and ``<hc>.mix`` [S, S] 
   u = sum_s in[s] x_s;   y = sublayer(norm(u));   x_r <- sum_s mix[s, r] x_s + out[r] y     (all r from the old streams)
 
 The read with its RMS norm and the write of the sublayer before it are one pass over the streams
-(``ops.streams_step``).  Mixers and feed-forwards keep their interface: they ADD their result into a zeroed fp32 row
-buffer, which the write then distributes.  A layer may have no feed-forward.  ``learned`` False (one stream only): no
+(``ops.streams_step``), also across layers: a layer leaves its last write to the first pass of the next one (the
+model carries out what the last layer left).  Mixers and feed-forwards keep their interface: their result goes into an fp32 row buffer
+(replacing what it held where the part can do that, added into zeroed rows otherwise), which the write then
+distributes.  A layer may have no feed-forward.  ``learned`` False (one stream only): no
 stream tensors are read and in = mix = out = 1, which is the plain pre-norm residual layer x <- x + sublayer(norm(x))
 through the same kernels.
 """
@@ -20,6 +22,18 @@ import torch
 from ..kernels import ops
 from .base import Block, TensorSpec
 from .plan import register_part
+
+
+# key of ``ctx.shared``: the last write of a layer, (y, mix, out), which the next layer's first pass over the streams
+# carries out (or ``flush_pending_write``, before anything else reads the streams)
+PENDING_WRITE = "residual_streams_pending_write"
+
+
+def flush_pending_write(ctx, h, streams: int) -> None:
+    """Carry out the write that the last layer left for its successor."""
+    pending = ctx.shared.pop(PENDING_WRITE, None)
+    if pending is not None:
+        ops.streams_step(h, streams, write=pending)
 
 
 class ResidualStreamsBlock(Block):
@@ -88,18 +102,31 @@ class ResidualStreamsBlock(Block):
         x = ctx.workspace.get("block_normed", (T, H), ctx.act_dtype)
         y = ctx.workspace.get("streams_sublayer_out", (T, H), torch.float32)
         in1, out1, mix1 = self.hc[0]
-        ops.streams_step(h, S, read=(in1, self.mixer_norm.weight, self.mixer_norm.eps, x))
-        y.zero_()
-        self.mixer.forward(x, y, ctx, cache, owns_cache)
+        # the write that the layer before left undone rides in this layer's first pass over the streams
+        pending = ctx.shared.pop(PENDING_WRITE, None)
+        # a mixer that reads its input shifted by a token lets the read do that where every request brings one token
+        ask = getattr(self.mixer, "shift_in_read", None)
+        shift = ask(ctx, cache, owns_cache) if ask is not None else None
+        ops.streams_step(h, S, write=pending, read=(in1, self.mixer_norm.weight, self.mixer_norm.eps, x),
+                         shift=None if shift is None else (shift[0], shift[1], ctx))
+        extra = {} if shift is None else {"shifted": True}
+        if getattr(self.mixer, "can_overwrite", False):
+            self.mixer.forward(x, y, ctx, cache, owns_cache, accumulate=False, **extra)
+        else:  # a mixer that only adds: into zeroed rows
+            y.zero_()
+            self.mixer.forward(x, y, ctx, cache, owns_cache, **extra)
         if self.feed_forward is None:
-            ops.streams_step(h, S, write=(y, mix1, out1))
+            ctx.shared[PENDING_WRITE] = (y, mix1, out1)
             return
         in2, out2, mix2 = self.hc[1]
         ops.streams_step(h, S, write=(y, mix1, out1),
                          read=(in2, self.feed_forward_norm.weight, self.feed_forward_norm.eps, x))
-        y.zero_()
-        self.feed_forward.forward(x, y, ctx)
-        ops.streams_step(h, S, write=(y, mix2, out2))
+        if getattr(self.feed_forward, "can_overwrite", False):
+            self.feed_forward.forward(x, y, ctx, accumulate=False)
+        else:
+            y.zero_()
+            self.feed_forward.forward(x, y, ctx)
+        ctx.shared[PENDING_WRITE] = (y, mix2, out2)
 
 
 register_part("block", "residual_streams", ResidualStreamsBlock)

@@ -31,6 +31,10 @@ class TokenShiftInput(Mixer):
     def graph_safe(self):
         return bool(getattr(self.inner, "graph_safe", False))
 
+    @property
+    def can_overwrite(self):
+        return bool(getattr(self.inner, "can_overwrite", False))
+
     def tensor_specs(self, prefix):
         return [TensorSpec(f"{prefix}.{self.weight_name}", (self.hidden_size,), "vector")] + \
             self.inner.tensor_specs(f"{prefix}.{self.inner_prefix}")
@@ -42,15 +46,30 @@ class TokenShiftInput(Mixer):
     def cache_need(self):
         return CombinedNeed((FixedState((self.hidden_size,), torch.float32), self.inner.cache_need()))
 
-    def forward(self, x, h, ctx, cache: LayerCache, owns_cache: bool):
+    def shift_in_read(self, ctx, cache: LayerCache, owns_cache: bool):
+        """(weights, state) if the caller's kernel that forms this mixer's input can shift it on its way (a step in which
+        every request brings one token, the state moved on as well), else None.  A caller that does so hands the rows to
+        ``forward`` with ``shifted=True``."""
+        if owns_cache and ctx.max_q_len == 1 and ctx.num_tokens == ctx.num_seqs:
+            return self.weight, cache.parts[0].state
+        return None
+
+    def forward(self, x, h, ctx, cache: LayerCache, owns_cache: bool, accumulate: bool = True, shifted: bool = False):
         last, inner_cache = cache.parts
-        u = ctx.workspace.get("token_shift_out", (x.shape[0], self.hidden_size), x.dtype)
-        ops.token_shift(x, u, self.weight, last.state, ctx, advance=owns_cache)
-        self.inner.forward(u, h, ctx, inner_cache, owns_cache)
+        if shifted:
+            u = x
+        else:
+            u = ctx.workspace.get("token_shift_out", (x.shape[0], self.hidden_size), x.dtype)
+            ops.token_shift(x, u, self.weight, last.state, ctx, advance=owns_cache)
+        if accumulate:
+            self.inner.forward(u, h, ctx, inner_cache, owns_cache)
+        else:
+            self.inner.forward(u, h, ctx, inner_cache, owns_cache, accumulate=False)
 
 
 class ParallelMixers(Mixer):
     accepts_lazy_norm = False
+    can_overwrite = True
 
     def __init__(self, hidden_size: int, branches: dict, norm_eps: float, coef: float = None, out_name: str = "out"):
         """``branches``: name -> PartSpec of a mixer (one to four), in order."""
@@ -81,13 +100,17 @@ class ParallelMixers(Mixer):
     def cache_need(self):
         return CombinedNeed(tuple(m.cache_need() for m in self.mixers))
 
-    def forward(self, x, h, ctx, cache: LayerCache, owns_cache: bool):
+    def forward(self, x, h, ctx, cache: LayerCache, owns_cache: bool, accumulate: bool = True):
         T = x.shape[0]
         results = ctx.workspace.get("parallel_mixers_out", (len(self.mixers), T, self.hidden_size), torch.float32)
-        results.zero_()  # every mixer adds its result into its own rows
         for i, m in enumerate(self.mixers):
-            m.forward(x, results[i], ctx, cache.parts[i], owns_cache)
-        ops.branch_norm_sum(h, [(results[i], w) for i, w in enumerate(self.out_weights)], self.coef, self.norm_eps)
+            if getattr(m, "can_overwrite", False):
+                m.forward(x, results[i], ctx, cache.parts[i], owns_cache, accumulate=False)
+            else:  # a mixer that only adds: into zeroed rows
+                results[i].zero_()
+                m.forward(x, results[i], ctx, cache.parts[i], owns_cache)
+        ops.branch_norm_sum(h, [(results[i], w) for i, w in enumerate(self.out_weights)], self.coef, self.norm_eps,
+                            accumulate=accumulate)
 
 
 register_part("mixer", "token_shift_input", TokenShiftInput)
