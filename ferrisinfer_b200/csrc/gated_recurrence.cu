@@ -230,7 +230,8 @@ __global__ void __launch_bounds__(GR_THREADS) gated_recurrence_kernel(
 
 // out = norm(o [* a(gate)]) * w [* a(gate)]: every `group` consecutive columns of a row divided by their own
 // sqrt(mean(.^2) + eps), times w[column % wlen]; the gate (a = sigmoid or SiLU) multiplies before the norm
-// (gate_first) or after it.  o fp32; gate and out in the activations' type.  A warp per group, a block per row.
+// (gate_first) or after it.  o fp32; gate and out in the activations' type.  A block per row; a warp per group, or
+// the whole block for each group in turn where groups are long.
 template <typename T>
 __global__ void __launch_bounds__(256) gated_group_norm_kernel(const float* o, int ldi, const T* gate, int ldg,
                                                                const float* __restrict__ w, int wlen, T* __restrict__ out,
@@ -243,6 +244,37 @@ __global__ void __launch_bounds__(256) gated_group_norm_kernel(const float* o, i
     const float* orow = o + (size_t)t * ldi;
     const T* grow = gate ? gate + (size_t)t * ldg : nullptr;
     T* dst = out + (size_t)t * ldo;
+    if (group >= 512) {  // few, long groups: the whole block takes them in turn
+        __shared__ float scratch[33];
+        for (int base = 0; base < n; base += group) {
+            float ss = 0.0f;
+            for (int i = threadIdx.x; i < group; i += blockDim.x) {
+                float val = orow[base + i];
+                if (grow && gate_first) {
+                    const float z = to_float(grow[base + i]);
+                    const float sg = 1.0f / (1.0f + expf(-z));
+                    val *= gate_kind == 1 ? z * sg : sg;
+                }
+                ss = fmaf(val, val, ss);
+            }
+            ss = block_sum(ss, scratch);
+            const float inv = 1.0f / sqrtf(ss / (float)group + eps);
+            for (int i = threadIdx.x; i < group; i += blockDim.x) {
+                float val = orow[base + i];
+                float gv = 1.0f;
+                if (grow) {
+                    const float z = to_float(grow[base + i]);
+                    const float sg = 1.0f / (1.0f + expf(-z));
+                    gv = gate_kind == 1 ? z * sg : sg;
+                }
+                if (gate_first) val *= gv;
+                float y = (val * inv) * w[(base + i) % wlen];
+                if (!gate_first) y *= gv;
+                dst[base + i] = from_float<T>(y);
+            }
+        }
+        return;
+    }
     for (int gi = warp; gi * group < n; gi += warps) {
         const int base = gi * group;
         float ss = 0.0f;
@@ -358,7 +390,7 @@ FERRIS_API int ferris_gated_group_norm(const float* o, int ldi, const void* gate
     if (n <= 0 || group <= 0 || n % group || wlen <= 0 || n % wlen) FERRIS_REFUSE("gated group norm: %d columns in groups of %d, %d weights", n, group, wlen);
     if (gate_kind != 0 && gate_kind != 1) FERRIS_REFUSE("gated group norm: unknown gate %d", gate_kind);
     const int groups = n / group;
-    const int threads = groups >= 8 ? 256 : (groups >= 4 ? 128 : (groups >= 2 ? 64 : 32));
+    const int threads = group >= 512 ? 256 : (groups >= 8 ? 256 : (groups >= 4 ? 128 : (groups >= 2 ? 64 : 32)));
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == FERRIS_F32)
         ferris_launch(gated_group_norm_kernel<float>, dim3(rows), dim3(threads), 0, s, o, ldi, (const float*)gate, ldg, w, wlen, (float*)out, ldo, n, group, eps, gate_kind, gate_first);

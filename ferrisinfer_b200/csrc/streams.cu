@@ -44,7 +44,7 @@ __global__ void __launch_bounds__(256) streams_sum_kernel(const float* xs, float
 // write (y not null): the streams take the sublayer's result; read (norm_w not null): out = rmsnorm(sum_s in[s] x_s) * norm_w.
 // mix, out_w, in_w lie in device memory (learned tensors), fp32.
 template <typename T>
-__global__ void __launch_bounds__(256) streams_step_kernel(float* xs, const float* y, const float* __restrict__ mix,
+__global__ void __launch_bounds__(512) streams_step_kernel(float* xs, const float* y, const float* __restrict__ mix,
                                                            const float* __restrict__ out_w, const float* __restrict__ in_w,
                                                            const float* __restrict__ norm_w, float eps, T* __restrict__ out,
                                                            int streams, int width, const float* __restrict__ shift,
@@ -265,7 +265,7 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(const T* proj, int 
 // Eight tokens of a head stand in shared memory (fp32); a thread owns an output column for all eight and reads
 // each weight once, consecutive threads consecutive columns.  fp32 FMAs, k ascending.
 // ---------------------------------------------------------------------------------------------
-constexpr int HG_TOKENS = 8, HG_THREADS = 128;
+constexpr int HG_TOKENS = 8, HG_THREADS = 64;
 
 template <typename T>
 __global__ void __launch_bounds__(HG_THREADS) head_gemm_kernel(const T* x, int ldx, int hsx, const T* __restrict__ w, T* __restrict__ out,
@@ -287,7 +287,8 @@ __global__ void __launch_bounds__(HG_THREADS) head_gemm_kernel(const T* x, int l
 #pragma unroll
     for (int r = 0; r < HG_TOKENS; ++r) acc[r] = 0.0f;
     const T* wh = w + (size_t)h * K * N + n;
-    for (int k = 0; k < K; ++k) {
+#pragma unroll 8
+    for (int k = 0; k < K; ++k) {  // unrolled: eight weights are on their way at a time
         const float wv = to_float(wh[(size_t)k * N]);
 #pragma unroll
         for (int r = 0; r < HG_TOKENS; ++r) acc[r] = fmaf(xs[r * K + k], wv, acc[r]);
@@ -333,7 +334,11 @@ FERRIS_API int ferris_streams_step(float* xs, const float* y, const float* mix, 
     if (shift && (!norm_w || !shift_state || !positions || !seq_state_slot)) FERRIS_REFUSE("streams: a token shift goes with a read, a state and the step's positions and slots");
     const size_t smem = norm_w ? (size_t)width * sizeof(float) : 0;
     cudaStream_t s = (cudaStream_t)stream;
-    const dim3 grid(tokens), block(width >= 1024 ? 256 : 128);
+    // A thread's columns are taken one after another (a column's stores stand between its loads and the next column's),
+    // so in a step of few rows a row is spread over as many threads as it has pairs of columns, up to 512; with many
+    // rows the SMs are busy anyway and blocks of 256 move more (2,048 rows of 4 x 2,048: 74 against 100 us).
+    const int wide = tokens < 256 ? 512 : 256;
+    const dim3 grid(tokens), block(width >= 1024 ? wide : (width >= 512 ? 256 : 128));
     if (dtype == FERRIS_F32) {
         int e_ = ferris_allow_dynamic_smem((const void*)streams_step_kernel<float>, smem);
         if (e_ != FERRIS_OK) return e_;
