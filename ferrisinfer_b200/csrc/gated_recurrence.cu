@@ -110,7 +110,9 @@ __global__ void __launch_bounds__(GR_THREADS) gated_recurrence_kernel(
     const float d_skip = skip ? skip[head] : 0.0f;
     // A stage's q, k, v and per-token numbers are requested into registers while the stage before it is worked on
     // (the requests of a stage are all in flight together), and go to shared memory when that one is done.
-    float pq[GR_STAGE][2], pk[GR_STAGE][2], pv[VP], pg = 0.0f, pb = 0.0f, pfq = 1.0f, pfk = 1.0f;
+    // (they stay as they were loaded until then: an instruction that touched one would wait for its load)
+    T pq[GR_STAGE][2], pk[GR_STAGE][2], pv[VP];
+    float pg = 0.0f, pb = 0.0f, pfq = 1.0f, pfk = 1.0f;
     auto request = [&](int t0) {
 #pragma unroll
         for (int r = 0; r < GR_STAGE; ++r) {
@@ -120,8 +122,8 @@ __global__ void __launch_bounds__(GR_THREADS) gated_recurrence_kernel(
             for (int j = 0; j < 2; ++j) {
                 const int c = tid + j * GR_THREADS;
                 if (c < dim) {
-                    pq[r][j] = to_float(q[row * ldq + (size_t)qh * dim + c]);
-                    pk[r][j] = to_float(k[row * ldk + (size_t)qh * dim + c]);
+                    pq[r][j] = q[row * ldq + (size_t)qh * dim + c];
+                    pk[r][j] = k[row * ldk + (size_t)qh * dim + c];
                 }
             }
         }
@@ -129,8 +131,8 @@ __global__ void __launch_bounds__(GR_THREADS) gated_recurrence_kernel(
         for (int j = 0; j < VP; ++j) {
             const int e = tid + j * GR_THREADS, r = e / COLS, c = e % COLS;
             const int cc = blockIdx.z * COLS + c;
-            pv[j] = 0.0f;
-            if (e < GR_STAGE * COLS && t0 + r < row1 && cc < vdim) pv[j] = to_float(v[(size_t)(t0 + r) * ldv + (size_t)head * vdim + cc]);
+            pv[j] = from_float<T>(0.0f);
+            if (e < GR_STAGE * COLS && t0 + r < row1 && cc < vdim) pv[j] = v[(size_t)(t0 + r) * ldv + (size_t)head * vdim + cc];
         }
         if (tid < GR_STAGE && t0 + tid < row1) {
             const size_t row = (size_t)(t0 + tid);
@@ -170,13 +172,13 @@ __global__ void __launch_bounds__(GR_THREADS) gated_recurrence_kernel(
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
                 const int c = tid + j * GR_THREADS;
-                if (c < dim) qs[r][c] = pq[r][j], ks[r][c] = pk[r][j];
+                if (c < dim) qs[r][c] = to_float(pq[r][j]), ks[r][c] = to_float(pk[r][j]);
             }
         }
 #pragma unroll
         for (int j = 0; j < VP; ++j) {
             const int e = tid + j * GR_THREADS;
-            if (e < n * COLS) (&vs[0][0])[e] = pv[j];
+            if (e < n * COLS) (&vs[0][0])[e] = to_float(pv[j]);
         }
         if (tid < GR_STAGE) gs[tid] = pg, bs[tid] = pb, fqs[tid] = pfq, fks[tid] = pfk;
         }
