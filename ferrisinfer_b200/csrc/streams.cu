@@ -262,41 +262,56 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(const T* proj, int 
 
 // ---------------------------------------------------------------------------------------------
 // A small product per head: out[t, h, n] = (sum_k x[t, h, k] W[h, k, n]) * g, g = 1 or sigmoid(gate[t, h]).
-// Eight tokens of a head stand in shared memory (fp32); a thread owns an output column for all eight and reads
-// each weight once, consecutive threads consecutive columns.  fp32 FMAs, k ascending.
+// Eight tokens of a head stand in shared memory (fp32); a thread owns an output column for all eight and a quarter
+// of the inputs, and reads each of its weights once, consecutive threads consecutive columns; the four quarters'
+// sums are added in order.  fp32 FMAs.
 // ---------------------------------------------------------------------------------------------
-constexpr int HG_TOKENS = 8, HG_THREADS = 64;
+constexpr int HG_TOKENS = 8, HG_COLS = 64, HG_PARTS = 4, HG_THREADS = HG_COLS * HG_PARTS;
 
 template <typename T>
 __global__ void __launch_bounds__(HG_THREADS) head_gemm_kernel(const T* x, int ldx, int hsx, const T* __restrict__ w, T* __restrict__ out,
                                                                int ldo, int hso, const T* gate, int ldg, int tokens, int K,
                                                                int N) {
-    extern __shared__ float xs[];  // [HG_TOKENS][K]
+    extern __shared__ float xs[];  // [HG_TOKENS][K], then the parts' sums [HG_PARTS - 1][HG_TOKENS][HG_COLS]
     pdl_wait();
     pdl_launch_dependents();
     const int t0 = blockIdx.x * HG_TOKENS, h = blockIdx.y;
-    const int n = blockIdx.z * HG_THREADS + threadIdx.x;
+    const int cl = threadIdx.x % HG_COLS, part = threadIdx.x / HG_COLS;
+    const int n = blockIdx.z * HG_COLS + cl;
     const int rows = tokens - t0 < HG_TOKENS ? tokens - t0 : HG_TOKENS;
     for (int i = threadIdx.x; i < HG_TOKENS * K; i += HG_THREADS) {
         const int r = i / K, k = i - r * K;
         xs[i] = r < rows ? to_float(x[(size_t)(t0 + r) * ldx + (size_t)h * hsx + k]) : 0.0f;
     }
     __syncthreads();
-    if (n >= N) return;
+    // the inputs are cut into four runs, a quarter of the block each: four times as many weights are on their way
     float acc[HG_TOKENS];
 #pragma unroll
     for (int r = 0; r < HG_TOKENS; ++r) acc[r] = 0.0f;
-    const T* wh = w + (size_t)h * K * N + n;
+    const int per = (K + HG_PARTS - 1) / HG_PARTS;
+    const int k0 = part * per, k1 = min(K, k0 + per);
+    if (n < N) {
+        const T* wh = w + (size_t)h * K * N + n;
 #pragma unroll 8
-    for (int k = 0; k < K; ++k) {  // unrolled: eight weights are on their way at a time
-        const float wv = to_float(wh[(size_t)k * N]);
+        for (int k = k0; k < k1; ++k) {
+            const float wv = to_float(wh[(size_t)k * N]);
 #pragma unroll
-        for (int r = 0; r < HG_TOKENS; ++r) acc[r] = fmaf(xs[r * K + k], wv, acc[r]);
+            for (int r = 0; r < HG_TOKENS; ++r) acc[r] = fmaf(xs[r * K + k], wv, acc[r]);
+        }
     }
+    float* sums = xs + HG_TOKENS * K;
+    if (part > 0) {
+#pragma unroll
+        for (int r = 0; r < HG_TOKENS; ++r) sums[((part - 1) * HG_TOKENS + r) * HG_COLS + cl] = acc[r];
+    }
+    __syncthreads();
+    if (part > 0 || n >= N) return;
 #pragma unroll
     for (int r = 0; r < HG_TOKENS; ++r) {
         if (r >= rows) break;
         float v = acc[r];
+#pragma unroll
+        for (int p = 0; p < HG_PARTS - 1; ++p) v += sums[(p * HG_TOKENS + r) * HG_COLS + cl];  // in the runs' order
         if (gate) v *= 1.0f / (1.0f + expf(-to_float(gate[(size_t)(t0 + r) * ldg + h])));
         out[(size_t)(t0 + r) * ldo + (size_t)h * hso + n] = from_float<T>(v);
     }
@@ -422,10 +437,10 @@ FERRIS_API int ferris_head_gemm(const void* x, int ldx, int hsx, const void* w, 
                                 const void* gate, int ldg, int dtype, int tokens, int heads, int K, int N, void* stream) {
     if (tokens <= 0) return FERRIS_OK;
     if (heads <= 0 || heads > 65535 || K <= 0 || N <= 0) FERRIS_REFUSE("head gemm: %d heads of %d x %d", heads, K, N);
-    const size_t smem = (size_t)HG_TOKENS * K * sizeof(float);
+    const size_t smem = ((size_t)HG_TOKENS * K + (size_t)(HG_PARTS - 1) * HG_TOKENS * HG_COLS) * sizeof(float);
     if (smem > 200 * 1024) FERRIS_REFUSE("head gemm: %d inputs a head are more than shared memory holds", K);
     cudaStream_t s = (cudaStream_t)stream;
-    const dim3 grid((tokens + HG_TOKENS - 1) / HG_TOKENS, heads, (N + HG_THREADS - 1) / HG_THREADS), block(HG_THREADS);
+    const dim3 grid((tokens + HG_TOKENS - 1) / HG_TOKENS, heads, (N + HG_COLS - 1) / HG_COLS), block(HG_THREADS);
     if (dtype == FERRIS_F32) {
         int e_ = ferris_allow_dynamic_smem((const void*)head_gemm_kernel<float>, smem);
         if (e_ != FERRIS_OK) return e_;
