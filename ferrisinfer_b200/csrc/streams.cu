@@ -216,12 +216,15 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(const T* proj, int 
                                                              T* __restrict__ q_att, int ldqa, int heads, int dim, int rot,
                                                              int rank, int write_kv) {
     __shared__ float scratch[33];
+    __shared__ float cs_tab[256], sn_tab[256];  // the token's angles, once for the key part and every head
     pdl_wait();
     pdl_launch_dependents();
     const int t = blockIdx.x;
     const float pos = (float)positions[t];
     const T* row = proj + (size_t)t * ld;
     const int half = rot_dims >> 1;
+    for (int f = threadIdx.x; f < half; f += blockDim.x) sincosf(pos * inv_freq[f], &sn_tab[f], &cs_tab[f]);
+    __syncthreads();
     // the heads' rotated query parts
     for (int i = threadIdx.x; i < heads * rot; i += blockDim.x) {
         const int h = i / rot, e = i - h * rot;
@@ -229,8 +232,7 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(const T* proj, int 
         float v = to_float(src[e]);
         if (e < rot_dims) {
             const int f = e < half ? e : e - half;
-            float sn, cs;
-            sincosf(pos * inv_freq[f], &sn, &cs);
+            const float sn = sn_tab[f], cs = cs_tab[f];
             const float other = to_float(src[e < half ? e + half : e - half]);
             v = e < half ? v * cs - other * sn : v * cs + other * sn;
         }
@@ -251,8 +253,7 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(const T* proj, int 
         float v = to_float(dkv[rank + e]);
         if (e < rot_dims) {
             const int f = e < half ? e : e - half;
-            float sn, cs;
-            sincosf(pos * inv_freq[f], &sn, &cs);
+            const float sn = sn_tab[f], cs = cs_tab[f];
             const float other = to_float(dkv[rank + (e < half ? e + half : e - half)]);
             v = e < half ? v * cs - other * sn : v * cs + other * sn;
         }
@@ -416,7 +417,7 @@ FERRIS_API int ferris_latent_prepare(const void* proj, int ld, int dtype, int q_
                                      int dim, int rot, int rank, int write_kv, void* stream) {
     if (tokens <= 0) return FERRIS_OK;
     if (heads <= 0 || dim < 0 || rot < 0 || rank <= 0) FERRIS_REFUSE("latent prepare: %d heads of %d + %d over a latent of %d", heads, dim, rot, rank);
-    if (rot_dims < 0 || rot_dims > rot || (rot_dims & 1)) FERRIS_REFUSE("latent prepare: %d of %d dimensions rotate", rot_dims, rot);
+    if (rot_dims < 0 || rot_dims > rot || (rot_dims & 1) || rot_dims > 512) FERRIS_REFUSE("latent prepare: %d of %d dimensions rotate (at most 512)", rot_dims, rot);
     if (rot_dims > 0 && !inv_freq) FERRIS_REFUSE("latent prepare: no frequencies");
     if (write_kv && (!slot_mapping || !cache || !norm_w)) FERRIS_REFUSE("latent prepare: no cache to write");
     cudaStream_t s = (cudaStream_t)stream;

@@ -654,3 +654,24 @@ def test_greedy_generation_through_the_engine(device, tmp_path, dtype):
         for i, tok in enumerate(ids):
             row = logits[len(prompt) + i - 1]
             assert row[tok] >= row.max() - slack * float(row.std()), (dtype, len(prompt), i, tok, int(row.argmax()))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replay_through_the_trace_runner(device, tmp_path, dtype):
+    """``bin/trace_run`` as a user runs it (a subprocess fed JSON lines, four state slots, just enough pages): a folder
+    of the design is chosen by its config.json, and a mixed schedule over six requests gives the plain logits."""
+    from test_trace_run_gpu import run_trace
+    from ferrisinfer_b200.weights.safetensors_io import write_safetensors
+
+    case = "B"
+    cfg, weights = cases.CASES[case], weights_of(case)
+    folder = str(tmp_path / "model")
+    os.makedirs(folder)
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    write_safetensors(os.path.join(folder, "model.safetensors"), weights)
+    lengths = {"a": (70, 31), "b": (33, 32), "c": (101, 33), "d": (48, 34), "e": (64, 35), "f": (90, 36)}
+    reqs = {n: wanted(case, *lengths[n])[0] for n in lengths}
+    steps = helpers.trace_mixed(reqs, seed=2)
+    got = run_trace(folder, dtype, steps, tmp_path / "out", helpers.tokens_held(steps), cfg["vocab"])
+    check_replay(got, lengths, case, dtype, "the trace runner")
