@@ -182,3 +182,28 @@ def row_errors(got: torch.Tensor, want: torch.Tensor) -> torch.Tensor:
 
 
 TOLERANCE = {"float32": 3e-5, "bfloat16": 5e-2}
+
+
+def random_config(rng: random.Random) -> dict:
+    """A configuration drawn at random: sizes, head counts, groupings, taps, streams, the order of the layers."""
+    divisor = lambda n: rng.choice([d for d in range(1, n + 1) if n % d == 0])
+    size = lambda: rng.choice([8, 16, 24, 32, 40, 64])
+    width = rng.choice([40, 48, 64, 72, 96])
+    layers = []
+    for _ in range(rng.randint(2, 5)):
+        kind = rng.choice(["delta", "latent", "parallel"])
+        ff = None if rng.random() < 0.2 else rng.choice([56, 64, 96, 128])
+        if kind == "delta":
+            heads = rng.choice([1, 2, 3, 4, 6])
+            layers.append(delta_layer(heads, divisor(heads), size(), size(), rng.randint(1, 4), ff))
+        elif kind == "latent":
+            rot = rng.choice([8, 16, 32])
+            layers.append(latent_layer(rng.randint(1, 6), size(), rot, size(), rng.choice([16, 24, 32, 64, 136]), ff,
+                                       base=rng.choice([100.0, 10000.0, 500000.0])))
+        else:
+            heads, rh, rv = rng.choice([1, 2, 4, 6]), rng.choice([1, 2, 3, 4, 8]), rng.choice([8, 16, 32])
+            layers.append(parallel_layer((heads, divisor(heads), size(), size()),
+                                         (rh, rv, rng.choice([8, 16, 24, 32, 64]), divisor(rh), divisor(rh) * rng.choice([1, 2]),
+                                          rng.randint(1, 4)), ff))
+    return config(layers, width=width, vocab=rng.randint(40, 200), streams=rng.choice([None, 1, 2, 3, 4, 6]),
+                  eps=rng.choice([1e-6, 1e-5]), scale=rng.choice([None, 3.0, 12.0]))

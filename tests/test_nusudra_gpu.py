@@ -675,3 +675,39 @@ def test_replay_through_the_trace_runner(device, tmp_path, dtype):
     steps = helpers.trace_mixed(reqs, seed=2)
     got = run_trace(folder, dtype, steps, tmp_path / "out", helpers.tokens_held(steps), cfg["vocab"])
     check_replay(got, lengths, case, dtype, "the trace runner")
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3, 4, 5, 6, 7, 8])
+def test_random_configuration_in_every_way_of_cutting(device, seed):
+    """Configurations drawn at random (sizes, head counts and groupings, taps, streams, the order and number of the
+    layers, pages of 4 to 32), replayed whole, with a decoded tail, in portions and in mixed batches, in 32-bit
+    against the plain implementation and in bfloat16 against the 32-bit run's tolerance class."""
+    import random
+
+    rng = random.Random(seed)
+    cfg = cases.random_config(rng)
+    weights = cases.make_weights(cfg, seed)
+    page = rng.choice([4, 8, 16, 16, 32])
+    lengths = [rng.randint(1, 40), rng.randint(20, 140), rng.randint(2, 70), rng.randint(60, 200), rng.randint(1, 20)]
+    reqs = {f"r{i}": cases.random_ids(cfg["vocab"], n, seed * 10 + i) for i, n in enumerate(lengths)}
+    want = {rid: plain.forward(cfg, weights, ids)[0] for rid, ids in reqs.items()}
+    traces = {"whole": helpers.trace_whole(reqs), "tail": helpers.trace_tail_decoded(reqs),
+              "portions": helpers.trace_portions(reqs), "mixed": helpers.trace_mixed(reqs, seed)}
+    for dtype in ("float32", "bfloat16"):
+        for kind, steps in traces.items():
+            pages = helpers.tokens_held(steps, round_to=page) // page
+            runner = make_runner(cfg, weights, dtype, device, num_pages=pages, max_requests=8, page_size=page)
+            got = helpers.replay(runner, steps)
+            runner.cache.check_invariants()
+            assert all(g.pool.num_used == 0 for g in runner.cache.groups)
+            worst, over, count = 0.0, 0, 0
+            for rid, ids in reqs.items():
+                rows = torch.stack([got[(rid, p)] for p in range(len(ids))])
+                assert torch.isfinite(rows).all(), (cfg, dtype, kind, rid)
+                err = cases.row_errors(rows, want[rid])
+                worst, over, count = max(worst, float(err.max())), over + int((err > cases.TOLERANCE[dtype]).sum()), count + len(ids)
+            if dtype == "float32":
+                assert worst <= cases.TOLERANCE[dtype], f"{cfg} page {page} {dtype} {kind}: {worst:.3g}"
+            else:
+                assert worst <= 4 * cases.TOLERANCE[dtype] and over <= max(1, count // 50), \
+                    f"{cfg} page {page} {dtype} {kind}: {worst:.3g}, {over} of {count} over"
