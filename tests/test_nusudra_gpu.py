@@ -711,3 +711,18 @@ def test_random_configuration_in_every_way_of_cutting(device, seed):
             else:
                 assert worst <= 4 * cases.TOLERANCE[dtype] and over <= max(1, count // 50), \
                     f"{cfg} page {page} {dtype} {kind}: {worst:.3g}, {over} of {count} over"
+
+
+def test_a_model_without_any_pages(device):
+    """Delta-rule layers only: no page group at all, state slots alone; portions and a decoded tail in 32-bit."""
+    cfg = cases.config([cases.delta_layer(2, 1, 16, 24, 3, 64), cases.delta_layer(3, 3, 8, 8, 2, None)], width=40, vocab=61,
+                       streams=2)
+    weights = cases.make_weights(cfg, 9)
+    ids = cases.random_ids(cfg["vocab"], 90, 4)
+    want = plain.forward(cfg, weights, ids)[0]
+    runner = make_runner(cfg, weights, "float32", device, num_pages=1, max_requests=2)
+    assert not runner.cache.groups
+    for steps in (helpers.trace_portions({"a": ids}), helpers.trace_tail_decoded({"a": ids}, tail=30)):
+        got = helpers.replay(runner, steps)
+        rows = torch.stack([got[("a", p)] for p in range(len(ids))])
+        assert float(cases.row_errors(rows, want).max()) <= cases.TOLERANCE["float32"]
